@@ -58,7 +58,8 @@ class CacheGroup:
             # zeros, not empty: a kernel may multiply a masked weight of 0 with whatever a page
             # holds beyond the sequence's end, and that has to be a finite number
             self.k = make("pages", (n, n_pages, needs.kv_heads, PAGE_TOKENS, needs.head_dim), dtype, True)
-            self.v = make("pages", (n, n_pages, needs.kv_heads, needs.head_dim, PAGE_TOKENS), dtype, True)
+            if needs.values:      # a lane of shared latents keeps one row per token, and no transposed twin
+                self.v = make("pages", (n, n_pages, needs.kv_heads, needs.head_dim, PAGE_TOKENS), dtype, True)
             if needs.pooled_stride > 0:
                 if PAGE_TOKENS % needs.pooled_stride:
                     raise ValueError(f"pooled-key stride {needs.pooled_stride} must divide the page size {PAGE_TOKENS}")
@@ -70,7 +71,7 @@ class CacheGroup:
     def bytes_per_token(self) -> int:
         if self.k is None:
             return 0
-        per = 2 * self.needs.kv_heads * self.needs.head_dim * self.k.element_size() * len(self.lanes)
+        per = (2 if self.needs.values else 1) * self.needs.kv_heads * self.needs.head_dim * self.k.element_size() * len(self.lanes)
         if self.pooled is not None:
             per += self.needs.kv_heads * self.needs.head_dim * 4 * len(self.lanes) // self.needs.pooled_stride
         return per

@@ -121,10 +121,8 @@ def write_random_folder(config_path: Optional[str], out_dir: str, seed: int, dty
         raise ValueError("--random-weights needs --config (a config.json to take the sizes from)")
     with open(config_path, "r", encoding="utf-8") as f:
         raw = json.load(f)
-    names = raw.get("architectures") or []
-    if not names:
-        raise ValueError(f"{config_path} names no architecture")
-    arch = architecture(names[0])
+    from .config.base import architecture_name
+    arch = architecture(architecture_name(raw))
     config = arch.config_class.from_dict(raw)
     specs = Model(arch.model_spec(config), None).weight_specs()
     folder = write_model_folder(config, specs, out_dir, int(seed), parse_dtype(dtype))

@@ -1,5 +1,6 @@
 from .base import ConfigError, FieldReader, architecture_name, read_config_json
 from .minicpm import MiniCPMConfig, RopeScaling, SparseConfig
+from .reravik import ReravikConfig
 
 __all__ = ["ConfigError", "FieldReader", "architecture_name", "read_config_json", "MiniCPMConfig", "RopeScaling",
-           "SparseConfig"]
+           "SparseConfig", "ReravikConfig"]

@@ -157,4 +157,7 @@ def architecture_name(data: Dict[str, Any]) -> str:
         return arch[0]
     if isinstance(arch, str):
         return arch
-    raise ConfigError("config.json: 'architectures' must be a non-empty list of names")
+    one = data.get("architecture")           # some configurations name their architecture with a single string
+    if arch is None and isinstance(one, str) and one:
+        return one
+    raise ConfigError("config.json: 'architectures' must be a non-empty list of names (or 'architecture' one name)")

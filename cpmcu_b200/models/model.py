@@ -11,8 +11,8 @@ from typing import Dict, List, Optional
 
 import torch
 
-from ..parts.base import (NORMS, Block, CacheNeeds, ModelSpec, ResidualStream, StepContext, WeightSpec, build_block,
-                          build_part)
+from ..parts.base import (NORMS, PASS_ENTRIES, Block, CacheNeeds, ModelSpec, ResidualStream, StepContext, WeightSpec,
+                          build_block, build_part)
 from ..parts.embedding import EMBEDDINGS, HEADS
 
 
@@ -24,6 +24,7 @@ class Model:
         self.blocks: List[Block] = [build_block(layer, ops) for layer in spec.layers]
         self.final_norm = build_part(NORMS, spec.final_norm, ops)
         self.head = build_part(HEADS, spec.head, ops)
+        self.pass_entry = build_part(PASS_ENTRIES, spec.pass_entry, ops) if spec.pass_entry is not None else None
         self.schedule = list(spec.schedule)
         for e in self.schedule:
             if not 0 <= e.layer < len(self.blocks):
@@ -45,6 +46,8 @@ class Model:
             yield layer.prefix, block
         yield self.spec.final_norm_name, self.final_norm
         yield self.spec.head_name, self.head
+        if self.pass_entry is not None:
+            yield self.spec.pass_entry_name, self.pass_entry
 
     def weight_specs(self) -> Dict[str, WeightSpec]:
         out: Dict[str, WeightSpec] = {}
@@ -66,9 +69,13 @@ class Model:
         total = sum(self.blocks[e.layer].weight_bytes() for e in self.schedule)
         return total + self.final_norm.weight_bytes() + self.head.weight_bytes()
 
+    def cache_bytes_per_step(self, kv_len: int) -> int:
+        """Bytes of cache and state a decode step of one sequence with ``kv_len`` keys has to read."""
+        return sum(self.blocks[e.layer].mixer.cache_bytes_read(kv_len) for e in self.schedule)
+
     def recordable_prompt(self) -> bool:
         """Whether every part can run a prompt chunk without reading the batch on the host (see Part)."""
-        parts = [self.embedding, self.final_norm, self.head]
+        parts = [self.embedding, self.final_norm, self.head] + ([self.pass_entry] if self.pass_entry is not None else [])
         for b in self.blocks:
             parts += [p for p in (b, b.mixer, b.feed_forward, b.mixer_norm, b.feed_forward_norm) if p is not None]
         return all(bool(getattr(p, "recordable_prompt", False)) for p in parts)
@@ -77,7 +84,7 @@ class Model:
     def cache_needs(self) -> List[CacheNeeds]:
         needs: List[Optional[CacheNeeds]] = [None] * self.spec.n_lanes()
         for e in self.schedule:
-            n = self.blocks[e.layer].mixer.cache_needs()
+            n = self.blocks[e.layer].cache_needs()
             if needs[e.lane] is None or e.writes_cache:
                 needs[e.lane] = n
         return [n if n is not None else CacheNeeds() for n in needs]
@@ -91,10 +98,20 @@ class Model:
         ops = self.ops
         if not ctx.extras.get("step_begun"):
             ops.begin_step()           # the caller did not lay out the step's workspace itself
-        stream = ResidualStream(ops, self.embedding.forward(ctx.token_ids))
+        stream = ResidualStream(ops, self.embedding.forward(ctx.token_ids, ctx.positions))
+        embedded = None
+        if self.pass_entry is not None:
+            # the stream as the embedding left it outlives the layers: it lies in the step's persistent part
+            embedded = ops.empty(*stream.x.shape, dtype=torch.float32)
+            embedded.copy_(stream.x)
+        taps = ctx.extras.get("taps")
         for k, e in enumerate(self.schedule):
             ops.begin_layer(k)         # this run's intermediates replace those of the run before the last
+            if e.enters_pass is not None and self.pass_entry is not None:
+                self.pass_entry.forward(ctx, stream, e.enters_pass, embedded)
             self.blocks[e.layer].forward(ctx, stream, ctx.cache.lane(e.lane), e.writes_cache)
+            if taps is not None and not ctx.captured and taps.get("streams") is not None:
+                taps["streams"].append(stream.flush().clone())      # a caller that wants the stream after every run
         ops.end_layers()
         if want_rows is None or want_rows.numel() == 0:
             return None

@@ -31,6 +31,10 @@ class _NoLibrary:
         return n_tokens * n_kv * (max_entries * 16 + n_slices * 32)
 
     @staticmethod
+    def cpm_mingru_summary_floats(n_tiles, width):
+        return n_tiles * 3 * width
+
+    @staticmethod
     def cpm_listed_attention_tcgen05_max_pages():
         return 11808
 

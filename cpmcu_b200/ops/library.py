@@ -50,10 +50,20 @@ _SIGNATURES = {
     "cpm_gemm_bf16_tcgen05_pair": [_P, _P, _P, c_int, c_int, c_int, c_int, c_int, _P],
     "cpm_listed_attention_tcgen05": [_P, _P, _P, _P, _P, _P, _P, _P, c_int, c_int, _P, c_int, c_int, c_int, c_int, c_int, c_float, _P],
     "cpm_sample_rows": [_P, c_int64, c_int, c_int, _P, _P, _P, c_uint64, _P, _P, _P],
+    "cpm_layernorm_rows": [_P, _P, _P, _P, _P, c_int, c_int, c_float, c_int, _P],
+    "cpm_layernorm_shift": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_float, c_int, _P],
+    "cpm_post_norm_add": [_P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_float, c_int, _P],
+    "cpm_stream_inject": [_P, _P, _P, c_int, c_int, _P],
+    "cpm_embed_sinusoid": [_P, _P, _P, _P, _P, c_int, c_int, c_float, c_int, _P],
+    "cpm_act_mul": [_P, _P, c_int, c_int, c_int, c_int, c_int, _P],
+    "cpm_mingru_scan": [_P, _P, _P, _P, _P, _P, _P, _P, _P, c_int, c_int, _P, _P, c_int, c_int, c_int, _P],
+    "cpm_latent_norm_store": [_P, _P, _P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_float, c_int, _P],
+    "cpm_head_project": [_P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P],
+    "cpm_latent_attention": [_P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_float, c_int, _P],
 }
 
 # source files whose kernels follow page tables; the checked build (CPMCU_CHECK_BOUNDS=1) keeps a record per file
-BOUNDS_FILES = ("attention_bf16", "attention_generic", "attention_tcgen05", "elementwise", "sparse")
+BOUNDS_FILES = ("attention_bf16", "attention_generic", "attention_tcgen05", "elementwise", "latent_attention", "sparse")
 
 _lock = threading.Lock()
 _lib: Optional[ctypes.CDLL] = None
@@ -114,6 +124,8 @@ def load() -> ctypes.CDLL:
         lib.cpm_listed_attention_tcgen05_max_pages.restype = c_int
         lib.cpm_decode_attention_scratch_floats.argtypes = [c_int, c_int, c_int, c_int, c_int]
         lib.cpm_decode_attention_scratch_floats.restype = c_int64
+        lib.cpm_mingru_summary_floats.argtypes = [c_int, c_int]
+        lib.cpm_mingru_summary_floats.restype = c_int64
         for name, argtypes in _SIGNATURES.items():
             try:
                 fn = getattr(lib, name)

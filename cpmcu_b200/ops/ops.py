@@ -170,6 +170,151 @@ class Ops:
         check(self.lib.cpm_silu_mul(_ptr(gu), _ptr(h), n, two_i // 2, interleave, self.code, self._stream()), "silu_mul")
         return h
 
+    # ---- layer norm, token shift, additions to the stream ----
+    def embed_sinusoid(self, ids: torch.Tensor, positions: torch.Tensor, table: torch.Tensor, freq: torch.Tensor,
+                       scale: float) -> torch.Tensor:
+        """fp32 [tokens, hidden] = table[ids] * scale + (sin | cos)(positions * freq), even entries sin, odd cos."""
+        self._i32(ids, "embed ids")
+        self._i32(positions, "positions")
+        self._act(table, "embedding table")
+        self._f32(freq, "frequencies")
+        n, hidden = ids.numel(), table.shape[1]
+        if freq.numel() * 2 != hidden:
+            raise ValueError("sinusoidal embedding: needs hidden/2 frequencies")
+        out = self.empty(n, hidden, dtype=torch.float32)
+        check(self.lib.cpm_embed_sinusoid(_ptr(ids), _ptr(positions), _ptr(table), _ptr(freq), _ptr(out), n, hidden,
+                                          float(scale), self.code, self._stream()), "embed_sinusoid")
+        return out
+
+    def layernorm(self, x: torch.Tensor, w: torch.Tensor, b: torch.Tensor, eps: float,
+                  rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """fp32 stream [tokens, hidden] -> (x - mean) / sqrt(var + eps) * w + b of all or of the listed rows."""
+        self._f32(x, "residual stream")
+        self._f32(w, "norm weight")
+        self._f32(b, "norm bias")
+        hidden = x.shape[-1]
+        n_rows = x.shape[0] if rows is None else rows.numel()
+        if rows is not None:
+            self._i32(rows, "norm rows")
+        y = self.empty(n_rows, hidden)
+        check(self.lib.cpm_layernorm_rows(_ptr(x), _ptr(w), _ptr(b), _ptr(y), _ptr(rows), n_rows, hidden, float(eps),
+                                          self.code, self._stream()), f"layernorm (hidden {hidden})")
+        return y
+
+    def layernorm_shift(self, ctx, x: torch.Tensor, w: torch.Tensor, b: torch.Tensor, eps: float, mix: torch.Tensor,
+                        state: torch.Tensor) -> torch.Tensor:
+        """h = layernorm(x); y_t = h_t + (h_{t-1} - h_t) * mix, with ``state`` [slots, hidden] fp32 giving the h before
+        a sequence's first token of the step and taking the h of its last."""
+        self._f32(x, "residual stream")
+        self._f32(state, "shift state")
+        for t, what in ((w, "norm weight"), (b, "norm bias"), (mix, "shift vector")):
+            self._f32(t, what)
+        n, hidden = x.shape
+        if state.shape[-1] != hidden:
+            raise ValueError("shift state does not match the hidden size")
+        y = self.empty(n, hidden)
+        check(self.lib.cpm_layernorm_shift(_ptr(x), _ptr(w), _ptr(b), _ptr(mix), _ptr(state), _ptr(ctx.positions),
+                                           _ptr(ctx.token_seq), _ptr(ctx.cu_q), _ptr(ctx.slot_dev), _ptr(y), n, hidden,
+                                           float(eps), self.code, self._stream()), f"layernorm_shift (hidden {hidden})")
+        return y
+
+    def post_norm_add(self, x: torch.Tensor, a: torch.Tensor, w: torch.Tensor, b: torch.Tensor, eps: float,
+                      then=None) -> Optional[torch.Tensor]:
+        """x += layernorm(a) with (w, b); ``then`` = (w2, b2): also returns layernorm(x) with those."""
+        self._f32(x, "residual stream")
+        self._act(a, "sublayer output")
+        if a.shape != x.shape:
+            raise ValueError(f"sublayer output {tuple(a.shape)} does not match the stream {tuple(x.shape)}")
+        n, hidden = x.shape
+        y = self.empty(n, hidden) if then is not None else None
+        w2, b2 = then if then is not None else (None, None)
+        check(self.lib.cpm_post_norm_add(_ptr(x), _ptr(a), _ptr(w), _ptr(b), _ptr(w2), _ptr(b2), _ptr(y), n, hidden,
+                                         float(eps), self.code, self._stream()), f"post_norm_add (hidden {hidden})")
+        return y
+
+    def stream_inject(self, x: torch.Tensor, saved: Optional[torch.Tensor], vec: Optional[torch.Tensor]) -> None:
+        """x += saved (same shape, fp32) + vec (one value per column, fp32); either may be None."""
+        self._f32(x, "residual stream")
+        if saved is not None and saved.shape != x.shape:
+            raise ValueError("saved stream does not match the stream")
+        if vec is not None and vec.numel() != x.shape[-1]:
+            raise ValueError("vector does not match the hidden size")
+        check(self.lib.cpm_stream_inject(_ptr(x), _ptr(saved), _ptr(vec), x.shape[0], x.shape[1], self._stream()),
+              "stream_inject")
+
+    # ---- recurrence ----
+    MINGRU_TILE_MIN_TOKENS = 32      # from this many tokens in a sequence on, a prompt's recurrence runs tile-parallel
+
+    def mingru_scan(self, ctx, proj: torch.Tensor, bz: torch.Tensor, bx: torch.Tensor, state: torch.Tensor,
+                    width: int) -> torch.Tensor:
+        """proj fp32 [tokens, 3*width] = [z | x | g] raw projections -> S_t * silu(g_t) [tokens, width], with the
+        per-sequence ``state`` [slots, width] fp32 read at a sequence's first token and written at its last."""
+        self._f32(proj, "recurrence projections")
+        self._f32(state, "recurrence state")
+        n = proj.shape[0]
+        if proj.shape[1] != 3 * width or state.shape[-1] != width:
+            raise ValueError("recurrence: projections must be [tokens, 3*width] and the state [slots, width]")
+        out = self.empty(n, width)
+        tiles = ctx.q_tiles
+        if ctx.is_decode or tiles is None or ctx.max_q_len < self.MINGRU_TILE_MIN_TOKENS:
+            check(self.lib.cpm_mingru_scan(_ptr(proj), _ptr(bz), _ptr(bx), _ptr(state), _ptr(ctx.positions), _ptr(ctx.cu_q),
+                                           _ptr(ctx.slot_dev), None, None, 0, 0, None, _ptr(out), ctx.n_seqs, width,
+                                           self.code, self._stream()), "mingru_scan")
+            return out
+        tile_seq, tile_row, n_tiles = tiles
+        summary = self.empty(int(self.lib.cpm_mingru_summary_floats(n_tiles, width)), dtype=torch.float32)
+        check(self.lib.cpm_mingru_scan(_ptr(proj), _ptr(bz), _ptr(bx), _ptr(state), _ptr(ctx.positions), _ptr(ctx.cu_q),
+                                       _ptr(ctx.slot_dev), _ptr(tile_seq), _ptr(tile_row), n_tiles, QUERY_TILE_TOKENS,
+                                       _ptr(summary), _ptr(out), ctx.n_seqs, width, self.code, self._stream()),
+              "mingru_scan (tiles)")
+        LAUNCHES_EXTRA[0] += 1
+        return out
+
+    # ---- attention over cached latents ----
+    def latent_norm_store(self, ctx, proj: torch.Tensor, g_q: torch.Tensor, g_kv: torch.Tensor, lane, q_rank: int,
+                          rank: int, eps: float, write_cache: bool = True) -> torch.Tensor:
+        """proj fp32 [tokens, q_rank + rank]: RMS-norms both parts; returns the query latent [tokens, q_rank] and
+        stores the key-value latent into the lane's pages at each token's position."""
+        self._f32(proj, "latent projections")
+        n = proj.shape[0]
+        if proj.shape[1] != q_rank + rank:
+            raise ValueError("latent projections must be [tokens, q_rank + rank]")
+        cq = self.empty(n, q_rank)
+        cache = lane.k if write_cache else None
+        check(self.lib.cpm_latent_norm_store(_ptr(proj), _ptr(g_q), _ptr(g_kv), _ptr(cq), _ptr(cache), _ptr(ctx.positions),
+                                             _ptr(ctx.token_seq), _ptr(ctx.slot_dev), _ptr(lane.page_table),
+                                             lane.page_table.shape[1], n, q_rank, rank, float(eps), self.code,
+                                             self._stream()), "latent_norm_store")
+        return cq
+
+    def head_project(self, x: torch.Tensor, w: torch.Tensor, n_heads: int, out_f32: bool) -> torch.Tensor:
+        """x [tokens, heads * k] (or [tokens, heads, k]; fp32 or the compute dtype) times w [heads, k, n] head by
+        head -> [tokens, heads, n], fp32 or the compute dtype."""
+        self._act(w, "per-head matrices")
+        n_tok = x.shape[0]
+        H, K, N = w.shape
+        if H != n_heads or x.numel() != n_tok * H * K or not x.is_contiguous():
+            raise ValueError(f"head_project: input {tuple(x.shape)} against matrices {tuple(w.shape)}")
+        in_f32 = x.dtype == torch.float32
+        if not in_f32 and x.dtype != self.dtype:
+            raise ValueError("head_project: the input must be fp32 or the compute dtype")
+        out = self.empty(n_tok, H, N, dtype=torch.float32 if out_f32 else self.dtype)
+        check(self.lib.cpm_head_project(_ptr(x), _ptr(w), _ptr(out), n_tok, H, K, N, 1 if in_f32 else 0,
+                                        1 if out_f32 else 0, self.code, self._stream()), f"head_project ({K} -> {N})")
+        return out
+
+    def latent_attention(self, ctx, q_lat: torch.Tensor, lane, scale: float, window: int = 0) -> torch.Tensor:
+        """q_lat fp32 [tokens, heads, rank] over the lane's cached latents (one row per token, shared by all heads
+        as key and as value) -> fp32 [tokens, heads, rank], the softmax-weighted sums of latents."""
+        self._f32(q_lat, "latent queries")
+        n, H, R = q_lat.shape
+        out = self.empty(n, H, R, dtype=torch.float32)
+        check(self.lib.cpm_latent_attention(_ptr(q_lat), _ptr(lane.k), _ptr(out), _ptr(ctx.positions), _ptr(ctx.token_seq),
+                                            _ptr(ctx.slot_dev), _ptr(lane.page_table), lane.page_table.shape[1], int(window),
+                                            n, H, R, float(scale), self.code, self._stream()),
+              f"latent attention (rank {R}, {H} heads)")
+        return out
+
     # ---- matrix products ----
     SKINNY_MAX_ROWS = int(os.environ.get("CPMCU_SKINNY_MAX_ROWS", "8"))   # most rows the weight-streaming product takes
     # From this many rows on the gated product runs on the tcgen05 kernel.  Its 128-row tiles are mostly empty for a
@@ -246,9 +391,21 @@ class Ops:
         """Error code the tcgen05 product kernel recorded since the last call (0 = none); synchronises."""
         return int(self.lib.cpm_gemm_tcgen05_error())
 
-    def gated_linear(self, a: torch.Tensor, w_gate_up: torch.Tensor, interleave: int) -> torch.Tensor:
-        """silu(a @ gate^T) * (a @ up^T) for a gate_up matrix [2*inter, K] laid out as ``interleave`` says."""
+    def act_mul(self, gu: torch.Tensor, interleave: int, activation: int) -> torch.Tensor:
+        """gu [tokens, 2*inter] -> act(gate) * up, [tokens, inter], for any activation code (0 SiLU, 1 tanh-GELU)."""
+        self._act(gu, "gate_up")
+        n, two_i = gu.shape
+        h = self.empty(n, two_i // 2)
+        check(self.lib.cpm_act_mul(_ptr(gu), _ptr(h), n, two_i // 2, interleave, int(activation), self.code, self._stream()),
+              "act_mul")
+        return h
+
+    def gated_linear(self, a: torch.Tensor, w_gate_up: torch.Tensor, interleave: int, activation: int = 0) -> torch.Tensor:
+        """act(a @ gate^T) * (a @ up^T) for a gate_up matrix [2*inter, K] laid out as ``interleave`` says; the
+        activation is SiLU (code 0) or the tanh form of GELU (code 1)."""
         M, K = a.shape
+        if activation != 0:
+            return self.act_mul(self.linear(a, w_gate_up), interleave, activation)
         if interleave == 8 and self._skinny_ok(M, K, w_gate_up.shape[0]) and w_gate_up.shape[0] % 16 == 0:
             self._act(a, "linear input")
             self._act(w_gate_up, "gate_up weight")

@@ -1,12 +1,12 @@
 """Parts a model is assembled from.  Importing this package registers the built-in ones."""
-from .base import (BLOCKS, FEED_FORWARDS, MIXERS, NORMS, POSITIONS, Block, CacheNeeds, FeedForward, LayerSpec,
+from .base import (BLOCKS, FEED_FORWARDS, MIXERS, NORMS, PASS_ENTRIES, POSITIONS, Block, PassEntry, CacheNeeds, FeedForward, LayerSpec,
                    Mixer, ModelSpec, Norm, Part, PartSpec, PositionEncoding, Registry, ResidualStream,
                    ScheduleEntry, StepContext, WeightSpec, build_block, build_part, default_schedule)
 from .embedding import EMBEDDINGS, HEADS
-from . import attention, block, feedforward, norm, position  # noqa: F401  (registration)
+from . import attention, block, feedforward, latent_attention, norm, position, recurrent, repeat  # noqa: F401  (registration)
 
 __all__ = [
-    "BLOCKS", "FEED_FORWARDS", "MIXERS", "NORMS", "POSITIONS", "EMBEDDINGS", "HEADS", "Block", "CacheNeeds",
+    "BLOCKS", "FEED_FORWARDS", "MIXERS", "NORMS", "PASS_ENTRIES", "PassEntry", "POSITIONS", "EMBEDDINGS", "HEADS", "Block", "CacheNeeds",
     "FeedForward", "LayerSpec", "Mixer", "ModelSpec", "Norm", "Part", "PartSpec", "PositionEncoding", "Registry",
     "ResidualStream", "ScheduleEntry", "StepContext", "WeightSpec", "build_block", "build_part",
     "default_schedule",

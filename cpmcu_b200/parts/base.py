@@ -97,6 +97,9 @@ class ScheduleEntry:
     layer: int
     lane: int
     writes_cache: bool = True
+    # When not None, a pass through a repeated group of layers begins with this run, and the number is the pass's
+    # (0, 1, ...): the model's ``pass_entry`` part then acts on the residual stream right before the run.
+    enters_pass: Optional[int] = None
 
 
 @dataclass(frozen=True)
@@ -114,6 +117,10 @@ class ModelSpec:
     head_name: str = "lm_head."
     stop_token_ids: Sequence[int] = ()
     max_positions: int = 0
+    # What happens to the residual stream where a run of the schedule ``enters_pass`` (None: nothing); its tensors
+    # are named below ``pass_entry_name``.
+    pass_entry: Optional[PartSpec] = None
+    pass_entry_name: str = ""
 
     def n_lanes(self) -> int:
         return 1 + max(e.lane for e in self.schedule)
@@ -143,8 +150,10 @@ class CacheNeeds:
     kv_heads/head_dim: one key row and one value row per token and key-value head
     (0 heads = none).  window: None if every key stays needed, else the number of
     most recent tokens that do.  pooled_stride/pooled_kernel: an extra row per
-    ``pooled_stride`` tokens (mean-pooled keys); 0 = none.  state: tensors of fixed
-    size per sequence, name -> (shape, dtype); they are zero when a sequence starts.
+    ``pooled_stride`` tokens (mean-pooled keys); 0 = none.  values: False when the
+    lane keeps key rows only (a shared latent that keys and values are both made
+    from).  state: tensors of fixed size per sequence, name -> (shape, dtype); they
+    are zero when a sequence starts.
     """
 
     kv_heads: int = 0
@@ -153,9 +162,19 @@ class CacheNeeds:
     pooled_stride: int = 0
     pooled_kernel: int = 0
     state: Mapping[str, Tuple[Tuple[int, ...], torch.dtype]] = field(default_factory=dict)
+    values: bool = True
 
     def group_key(self) -> Tuple:
-        return (self.kv_heads, self.head_dim, self.window, self.pooled_stride, self.pooled_kernel)
+        return (self.kv_heads, self.head_dim, self.window, self.pooled_stride, self.pooled_kernel, self.values)
+
+    def with_state(self, more: Mapping[str, Tuple[Tuple[int, ...], torch.dtype]]) -> "CacheNeeds":
+        """The same needs with further per-sequence tensors (a block adds its own to its mixer's)."""
+        both = dict(self.state)
+        for name, what in more.items():
+            if name in both:
+                raise ValueError(f"per-sequence state '{name}' is declared twice for one lane")
+            both[name] = what
+        return CacheNeeds(self.kv_heads, self.head_dim, self.window, self.pooled_stride, self.pooled_kernel, both, self.values)
 
 
 # ---------------------------------------------------------------------------
@@ -304,6 +323,11 @@ class Block(Part):
     def weight_bytes(self) -> int:
         return sum(p.weight_bytes() for _, p in self.sub_parts())
 
+    def cache_needs(self) -> CacheNeeds:
+        """What a run of this layer keeps per sequence: its mixer's needs, plus whatever the arrangement itself
+        carries from token to token."""
+        return self.mixer.cache_needs()
+
     def forward(self, ctx: "StepContext", stream: ResidualStream, lane, writes_cache: bool) -> None:
         raise NotImplementedError
 
@@ -313,6 +337,17 @@ FEED_FORWARDS: Registry[Type[FeedForward]] = Registry("feed-forward")
 NORMS: Registry[Type[Norm]] = Registry("norm")
 POSITIONS: Registry[Type[PositionEncoding]] = Registry("position encoding")
 BLOCKS: Registry[Type[Block]] = Registry("block")
+
+
+class PassEntry(Part):
+    """Acts on the residual stream where a pass through a repeated group of layers begins."""
+
+    def forward(self, ctx: "StepContext", stream: ResidualStream, number: int, embedded: torch.Tensor) -> None:
+        """``number``: the pass's (0, 1, ...); ``embedded``: the stream as the embedding left it (fp32, read only)."""
+        raise NotImplementedError
+
+
+PASS_ENTRIES: Registry[Type[PassEntry]] = Registry("pass entry")
 
 
 def build_part(registry: Registry, spec: PartSpec, ops):

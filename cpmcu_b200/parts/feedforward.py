@@ -12,15 +12,21 @@ import torch
 
 from .base import FEED_FORWARDS, FeedForward, WeightSpec
 
+ACTIVATIONS = {"silu": 0, "gelu_tanh": 1}      # the codes of the activation kernels (csrc/activation.cu)
+
 
 @FEED_FORWARDS.register("gated_ffn")
 class GatedFeedForward(FeedForward):
     recordable_prompt = True
 
-    def __init__(self, ops, hidden_size: int, intermediate_size: int, activation: str = "silu"):
+    def __init__(self, ops, hidden_size: int, intermediate_size: int, activation: str = "silu", names=None):
+        """``activation``: "silu", or "gelu_tanh" (0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))).  ``names``: the three
+        matrices' names below the part's prefix, by "gate", "up" and "down" (default: the reference's)."""
         super().__init__(ops)
-        if activation != "silu":
-            raise ValueError(f"gated_ffn: activation '{activation}' is not built; known: ['silu']")
+        if activation not in ACTIVATIONS:
+            raise ValueError(f"gated_ffn: activation '{activation}' is not built; known: {sorted(ACTIVATIONS)}")
+        self.activation = ACTIVATIONS[activation]
+        self.names = dict(names) if names else {}
         self.hidden_size = int(hidden_size)
         self.intermediate_size = int(intermediate_size)
         self.interleave = 0
@@ -30,13 +36,16 @@ class GatedFeedForward(FeedForward):
     def weight_specs(self) -> Dict[str, WeightSpec]:
         i, h = self.intermediate_size, self.hidden_size
         return {
-            "gate_proj.weight": WeightSpec((i, h)),
-            "up_proj.weight": WeightSpec((i, h)),
-            "down_proj.weight": WeightSpec((h, i)),
+            self._name("gate"): WeightSpec((i, h)),
+            self._name("up"): WeightSpec((i, h)),
+            self._name("down"): WeightSpec((h, i)),
         }
 
+    def _name(self, which: str) -> str:
+        return self.names.get(which, which + "_proj.weight")
+
     def load_weights(self, tensors: Dict[str, torch.Tensor]) -> None:
-        gate, up = tensors["gate_proj.weight"], tensors["up_proj.weight"]
+        gate, up = tensors[self._name("gate")], tensors[self._name("up")]
         i, h = self.intermediate_size, self.hidden_size
         if i % 8 == 0:
             # blocks of 8 gate rows followed by the 8 up rows of the same features: gate and up of a
@@ -47,11 +56,11 @@ class GatedFeedForward(FeedForward):
             self.interleave = 0
             self.w_gate_up = torch.cat([gate, up], dim=0).contiguous()
         self.w_gate_up = self.ops.keep(self.w_gate_up)
-        self.w_down = self.ops.keep(tensors["down_proj.weight"].contiguous())
+        self.w_down = self.ops.keep(tensors[self._name("down")].contiguous())
 
     def weight_bytes(self) -> int:
         return (self.w_gate_up.numel() + self.w_down.numel()) * self.w_gate_up.element_size()
 
     def forward(self, ctx, y: torch.Tensor) -> torch.Tensor:
-        h = self.ops.gated_linear(y, self.w_gate_up, self.interleave)
+        h = self.ops.gated_linear(y, self.w_gate_up, self.interleave, self.activation)
         return self.ops.linear(h, self.w_down)

@@ -87,6 +87,10 @@ def _register_builtin() -> None:
         adapt_tensor=minicpm4.split_fused_tensors,
         ignore_tensor=minicpm4.ignored_tensor,
     ))
+    from .config.reravik import ReravikConfig
+    from .models import reravik
+
+    register_architecture(Architecture(name=ReravikConfig.architecture, config_class=ReravikConfig, model_spec=reravik.model_spec))
 
 
 _register_builtin()
