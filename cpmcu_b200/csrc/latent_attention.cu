@@ -236,4 +236,248 @@ CPM_API int cpm_latent_attention(const float* q, const void* cache, float* out, 
 #undef CPM_LATENT
 }
 
+// ---------------------------------------------------------------------------
+// The same attention on the tensor cores, for bf16 latents (mma.sync m16n8k16, fp32 accumulation).  A block is one
+// token, up to 16 heads (the 16 rows of the tile) and one share of the token's keys; its four warps split the work
+// of every tile of 32 latent rows twice: for the scores each warp takes 8 of the 32 keys over the whole rank, for the
+// weighted sum each warp takes every fourth group of 8 latent columns over all 32 keys, the latent tile being read
+// as the "key" operand straight from its rows and as the "value" operand through ldmatrix.trans.  Scores go through
+// shared memory in fp32; the softmax statistics are kept by every warp alike.  With more than one share a block
+// leaves (max, sum, unnormalised output) in scratch and a second kernel merges the shares.
+constexpr int kMmaKeys = 32;
+constexpr int kMmaRows = 16;
+
+__device__ __forceinline__ void mma_bf16_16816(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&v);
+}
+
+// NT: column groups of 8 a warp may own (rank <= 32 * NT).  scratch per (token, head group, share): 16 * (rank + 2) floats.
+template <int NT>
+__global__ void __launch_bounds__(128)
+latent_attention_mma_kernel(const float* __restrict__ q, const bf16* __restrict__ cache, float* __restrict__ out,
+                            float* __restrict__ scratch, const int* __restrict__ positions, const int* __restrict__ token_seq,
+                            const int* __restrict__ slots, const int* __restrict__ page_table, int max_pages, int window,
+                            int n_heads, int rank, float scale, int n_splits) {
+    extern __shared__ __align__(16) unsigned char lm_smem[];
+    const int pitch = rank + 8;                                          // bf16 elements per row of Qs and Ks
+    bf16* Qs = reinterpret_cast<bf16*>(lm_smem);                         // [16][pitch]
+    bf16* Ks = Qs + kMmaRows * pitch;                                    // [32][pitch]
+    float* Ss = reinterpret_cast<float*>(Ks + kMmaKeys * pitch);         // [16][33]
+    pdl_launch_dependents();
+    pdl_wait();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, tg = lane & 3;
+    const int t = blockIdx.x, h0 = blockIdx.y * kMmaRows, split = blockIdx.z;
+    const int p = positions[t];
+    const int* pages = page_table + (int64_t)slots[token_seq[t]] * max_pages;
+    const int lo = window > 0 ? max(0, p - window + 1) : 0;
+    const int tiles_total = (p + 1 - lo + kMmaKeys - 1) / kMmaKeys;
+    const int per = (tiles_total + n_splits - 1) / n_splits;
+    const int tile0 = split * per, tile1 = min(tiles_total, tile0 + per);
+
+    for (int i = threadIdx.x; i < kMmaRows * rank; i += blockDim.x) {
+        const int r = i / rank, c = i % rank;
+        const int h = h0 + r;
+        Qs[r * pitch + c] = __float2bfloat16_rn(h < n_heads ? q[((int64_t)t * n_heads + h) * rank + c] : 0.f);
+    }
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};             // rows g and g + 8
+    float acc[NT][4];
+#pragma unroll
+    for (int i = 0; i < NT; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
+    const int k_steps = rank / 16;
+    const int vec_per_row = rank / 8;                                    // 16-byte pieces of a latent row
+
+    for (int tile = tile0; tile < tile1; ++tile) {
+        const int j0 = lo + tile * kMmaKeys;
+        __syncthreads();                                                 // Ks, Ss of the tile before are no longer read
+        for (int i = threadIdx.x; i < kMmaKeys * vec_per_row; i += blockDim.x) {
+            const int r = i / vec_per_row, v = i % vec_per_row;
+            const int j = j0 + r;
+            uint4 val = make_uint4(0u, 0u, 0u, 0u);
+            if (j <= p) {
+                const int page = CPM_PAGE(pages, j / kPageTokens, max_pages);
+                val = *reinterpret_cast<const uint4*>(cache + page_row_offset(page, 0, j % kPageTokens, 1, rank) + 8 * v);
+            }
+            *reinterpret_cast<uint4*>(Ks + r * pitch + 8 * v) = val;
+        }
+        __syncthreads();
+        {   // scores of keys 8 * warp .. + 8 for all 16 rows
+            float c[4] = {0.f, 0.f, 0.f, 0.f};
+            const bf16* krow = Ks + (8 * warp + g) * pitch;
+            for (int ks = 0; ks < k_steps; ++ks) {
+                uint32_t a[4];
+                const bf16* q0 = Qs + g * pitch + ks * 16 + 2 * tg;
+                a[0] = *reinterpret_cast<const uint32_t*>(q0);
+                a[1] = *reinterpret_cast<const uint32_t*>(q0 + 8 * pitch);
+                a[2] = *reinterpret_cast<const uint32_t*>(q0 + 8);
+                a[3] = *reinterpret_cast<const uint32_t*>(q0 + 8 * pitch + 8);
+                const uint32_t b0 = *reinterpret_cast<const uint32_t*>(krow + ks * 16 + 2 * tg);
+                const uint32_t b1 = *reinterpret_cast<const uint32_t*>(krow + ks * 16 + 8 + 2 * tg);
+                mma_bf16_16816(c, a, b0, b1);
+            }
+            const int col = 8 * warp + 2 * tg;
+            const bool ok0 = j0 + col <= p, ok1 = j0 + col + 1 <= p;
+            Ss[g * 33 + col] = ok0 ? c[0] * scale : -INFINITY;
+            Ss[g * 33 + col + 1] = ok1 ? c[1] * scale : -INFINITY;
+            Ss[(g + 8) * 33 + col] = ok0 ? c[2] * scale : -INFINITY;
+            Ss[(g + 8) * 33 + col + 1] = ok1 ? c[3] * scale : -INFINITY;
+        }
+        __syncthreads();
+        // softmax of the tile, kept by every warp alike; a thread holds, for rows g and g + 8, the columns
+        // 2tg, 2tg+1, 2tg+8, 2tg+9 of both halves of 16 keys: its A fragments of the weighted sum
+        float s[2][2][4];
+#pragma unroll
+        for (int half = 0; half < 2; ++half)
+#pragma unroll
+            for (int r = 0; r < 2; ++r) {
+                const float* row = Ss + (g + 8 * r) * 33 + 16 * half + 2 * tg;
+                s[half][r][0] = row[0]; s[half][r][1] = row[1]; s[half][r][2] = row[8]; s[half][r][3] = row[9];
+            }
+        uint32_t pa[2][4];
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            float mx = -INFINITY;
+#pragma unroll
+            for (int half = 0; half < 2; ++half)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) mx = fmaxf(mx, s[half][r][e]);
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+            const float m_new = fmaxf(m[r], mx);
+            const float corr = (m[r] == -INFINITY) ? 0.f : expf(m[r] - m_new);
+            float sum = 0.f;
+#pragma unroll
+            for (int half = 0; half < 2; ++half)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float pv = (m_new == -INFINITY) ? 0.f : expf(s[half][r][e] - m_new);
+                    s[half][r][e] = pv;
+                    sum += pv;
+                }
+            sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+            sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+            l[r] = l[r] * corr + sum;
+            m[r] = m_new;
+#pragma unroll
+            for (int i = 0; i < NT; ++i) { acc[i][2 * r] *= corr; acc[i][2 * r + 1] *= corr; }
+        }
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            pa[half][0] = pack_bf16(s[half][0][0], s[half][0][1]);      // row g,     keys 2tg, 2tg+1
+            pa[half][1] = pack_bf16(s[half][1][0], s[half][1][1]);      // row g + 8
+            pa[half][2] = pack_bf16(s[half][0][2], s[half][0][3]);      // row g,     keys 2tg+8, 2tg+9
+            pa[half][3] = pack_bf16(s[half][1][2], s[half][1][3]);      // row g + 8
+        }
+#pragma unroll
+        for (int i = 0; i < NT; ++i) {
+            const int col0 = 8 * (warp + 4 * i);
+            if (col0 < rank) {
+#pragma unroll
+                for (int half = 0; half < 2; ++half) {
+                    uint32_t b0, b1;
+                    const uint32_t addr = (uint32_t)__cvta_generic_to_shared(Ks + (16 * half + (lane & 15)) * pitch + col0);
+                    asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];" : "=r"(b0), "=r"(b1) : "r"(addr));
+                    mma_bf16_16816(acc[i], pa[half], b0, b1);
+                }
+            }
+        }
+    }
+    // rows g and g + 8 are heads h0 + g and h0 + g + 8; a thread holds columns col0 + 2tg, + 1 of its column groups
+    if (n_splits == 1) {
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            const int h = h0 + g + 8 * r;
+            if (h >= n_heads) continue;
+            const float inv = l[r] > 0.f ? 1.f / l[r] : 0.f;
+            float* orow = out + ((int64_t)t * n_heads + h) * rank;
+#pragma unroll
+            for (int i = 0; i < NT; ++i) {
+                const int c = 8 * (warp + 4 * i) + 2 * tg;
+                if (c < rank) *reinterpret_cast<float2*>(orow + c) = make_float2(acc[i][2 * r] * inv, acc[i][2 * r + 1] * inv);
+            }
+        }
+        return;
+    }
+    float* part = scratch + (((int64_t)t * gridDim.y + blockIdx.y) * n_splits + split) * kMmaRows * (rank + 2);
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        float* prow = part + (g + 8 * r) * (rank + 2);
+        if (warp == 0 && tg == 0) { prow[rank] = m[r]; prow[rank + 1] = l[r]; }
+#pragma unroll
+        for (int i = 0; i < NT; ++i) {
+            const int c = 8 * (warp + 4 * i) + 2 * tg;
+            if (c < rank) { prow[c] = acc[i][2 * r]; prow[c + 1] = acc[i][2 * r + 1]; }
+        }
+    }
+}
+
+__global__ void latent_attention_merge_kernel(const float* __restrict__ scratch, float* __restrict__ out, int n_heads, int rank,
+                                              int n_splits) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.x, hg = blockIdx.y;
+    const float* base = scratch + ((int64_t)t * gridDim.y + hg) * n_splits * kMmaRows * (rank + 2);
+    for (int i = threadIdx.x; i < kMmaRows * rank; i += blockDim.x) {
+        const int r = i / rank, c = i % rank;
+        const int h = hg * kMmaRows + r;
+        if (h >= n_heads) continue;
+        float mx = -INFINITY;
+        for (int s = 0; s < n_splits; ++s) mx = fmaxf(mx, base[(s * kMmaRows + r) * (rank + 2) + rank]);
+        float l = 0.f, o = 0.f;
+        for (int s = 0; s < n_splits; ++s) {
+            const float* prow = base + (s * kMmaRows + r) * (rank + 2);
+            const float w = prow[rank] == -INFINITY ? 0.f : expf(prow[rank] - mx);
+            l = fmaf(prow[rank + 1], w, l);
+            o = fmaf(prow[c], w, o);
+        }
+        out[((int64_t)t * n_heads + h) * rank + c] = l > 0.f ? o / l : 0.f;
+    }
+}
+
+CPM_API int64_t cpm_latent_attention_scratch_floats(int n_tokens, int n_heads, int rank, int n_splits) {
+    if (n_splits <= 1) return 0;
+    return (int64_t)n_tokens * ((n_heads + kMmaRows - 1) / kMmaRows) * n_splits * kMmaRows * (rank + 2);
+}
+
+template <int NT>
+static int launch_latent_mma(const float* q, const void* cache, float* out, float* scratch, const int* positions,
+                             const int* token_seq, const int* slots, const int* page_table, int max_pages, int window,
+                             int n_tokens, int n_heads, int rank, float scale, int n_splits, cudaStream_t stream) {
+    static bool smem_done[kMaxDevices];
+    const size_t smem = (size_t)(kMmaRows + kMmaKeys) * (rank + 8) * sizeof(bf16) + (size_t)kMmaRows * 33 * sizeof(float);
+    auto kern = latent_attention_mma_kernel<NT>;
+    if (smem > 48 * 1024)
+        if (int e = ensure_dynamic_smem(kern, (int)smem, smem_done)) return e;
+    const int groups = (n_heads + kMmaRows - 1) / kMmaRows;
+    dim3 grid(n_tokens, groups, n_splits);
+    cpm_launch(kLaunchAttention, kern, grid, 128, smem, stream, q, (const bf16*)cache, out, scratch, positions, token_seq, slots,
+               page_table, max_pages, window, n_heads, rank, scale, n_splits);
+    if (n_splits > 1)
+        cpm_launch(kLaunchCombine, latent_attention_merge_kernel, dim3(n_tokens, groups), 256, 0, stream, (const float*)scratch, out,
+                   n_heads, rank, n_splits);
+    return launch_status();
+}
+
+// bf16 latents, rank a multiple of 16 up to 512; ``scratch``: cpm_latent_attention_scratch_floats floats when n_splits > 1.
+CPM_API int cpm_latent_attention_mma(const float* q, const void* cache, float* out, float* scratch, const int* positions,
+                                     const int* token_seq, const int* slots, const int* page_table, int max_pages, int window,
+                                     int n_tokens, int n_heads, int rank, float scale, int n_splits, cudaStream_t stream) {
+    if (n_tokens <= 0) return CPM_OK;
+    if (n_heads <= 0 || rank <= 0 || rank > 512 || rank % 16 || window < 0 || n_splits < 1 || n_splits > 65535) return CPM_BAD_ARGUMENT;
+    if (n_splits > 1 && scratch == nullptr) return CPM_BAD_ARGUMENT;
+    if ((n_heads + kMmaRows - 1) / kMmaRows > 65535) return CPM_BAD_ARGUMENT;
+    if (rank <= 128) return launch_latent_mma<4>(q, cache, out, scratch, positions, token_seq, slots, page_table, max_pages, window,
+                                                  n_tokens, n_heads, rank, scale, n_splits, stream);
+    if (rank <= 256) return launch_latent_mma<8>(q, cache, out, scratch, positions, token_seq, slots, page_table, max_pages, window,
+                                                  n_tokens, n_heads, rank, scale, n_splits, stream);
+    return launch_latent_mma<16>(q, cache, out, scratch, positions, token_seq, slots, page_table, max_pages, window, n_tokens,
+                                 n_heads, rank, scale, n_splits, stream);
+}
+
 CPM_BOUNDS_TU(latent_attention)

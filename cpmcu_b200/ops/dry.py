@@ -31,6 +31,10 @@ class _NoLibrary:
         return n_tokens * n_kv * (max_entries * 16 + n_slices * 32)
 
     @staticmethod
+    def cpm_latent_attention_scratch_floats(n_tokens, n_heads, rank, n_splits):
+        return 0 if n_splits <= 1 else n_tokens * ((n_heads + 15) // 16) * n_splits * 16 * (rank + 2)
+
+    @staticmethod
     def cpm_mingru_summary_floats(n_tiles, width):
         return n_tiles * 3 * width
 

@@ -60,6 +60,7 @@ _SIGNATURES = {
     "cpm_latent_norm_store": [_P, _P, _P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_float, c_int, _P],
     "cpm_head_project": [_P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P],
     "cpm_latent_attention": [_P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_float, c_int, _P],
+    "cpm_latent_attention_mma": [_P, _P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_float, c_int, _P],
 }
 
 # source files whose kernels follow page tables; the checked build (CPMCU_CHECK_BOUNDS=1) keeps a record per file
@@ -124,6 +125,8 @@ def load() -> ctypes.CDLL:
         lib.cpm_listed_attention_tcgen05_max_pages.restype = c_int
         lib.cpm_decode_attention_scratch_floats.argtypes = [c_int, c_int, c_int, c_int, c_int]
         lib.cpm_decode_attention_scratch_floats.restype = c_int64
+        lib.cpm_latent_attention_scratch_floats.argtypes = [c_int, c_int, c_int, c_int]
+        lib.cpm_latent_attention_scratch_floats.restype = c_int64
         lib.cpm_mingru_summary_floats.argtypes = [c_int, c_int]
         lib.cpm_mingru_summary_floats.restype = c_int64
         for name, argtypes in _SIGNATURES.items():

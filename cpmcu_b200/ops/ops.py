@@ -303,12 +303,39 @@ class Ops:
                                         1 if out_f32 else 0, self.code, self._stream()), f"head_project ({K} -> {N})")
         return out
 
-    def latent_attention(self, ctx, q_lat: torch.Tensor, lane, scale: float, window: int = 0) -> torch.Tensor:
+    def latent_attention_splits(self, ctx, n_tokens: int, n_heads: int, window: int) -> int:
+        """How many blocks share the keys of one token and head group in the tensor-core kernel: one, unless the step's
+        tokens leave most SMs idle (a decode step) and there are enough keys (at least four tiles of 32 per share)."""
+        blocks = n_tokens * ((n_heads + 15) // 16)
+        if blocks * 2 > self.sm_count:
+            return 1
+        keys = min(window, ctx.max_kv_len) if window else ctx.max_kv_len      # in a recorded step an upper bound
+        return max(1, min(16, self.sm_count // blocks, ((keys + 31) // 32) // 4))
+
+    def latent_attention(self, ctx, q_lat: torch.Tensor, lane, scale: float, window: int = 0,
+                         n_splits: Optional[int] = None, tensor_cores: Optional[bool] = None) -> torch.Tensor:
         """q_lat fp32 [tokens, heads, rank] over the lane's cached latents (one row per token, shared by all heads
-        as key and as value) -> fp32 [tokens, heads, rank], the softmax-weighted sums of latents."""
+        as key and as value) -> fp32 [tokens, heads, rank], the softmax-weighted sums of latents.  bf16 latents of a
+        rank that is a multiple of 16 go to the tensor-core kernel (``tensor_cores`` False keeps the fp32 kernel)."""
         self._f32(q_lat, "latent queries")
         n, H, R = q_lat.shape
         out = self.empty(n, H, R, dtype=torch.float32)
+        mma_ok = self.code == BF16 and R % 16 == 0 and R <= 512
+        if tensor_cores and not mma_ok:
+            raise ValueError("the tensor-core latent attention takes bf16 latents of a rank that is a multiple of 16 up to 512")
+        if mma_ok and tensor_cores is not False:
+            if n_splits is None:
+                n_splits = self.latent_attention_splits(ctx, n, H, int(window))
+            scratch = None
+            if n_splits > 1:
+                scratch = self.empty(int(self.lib.cpm_latent_attention_scratch_floats(n, H, R, n_splits)), dtype=torch.float32)
+            check(self.lib.cpm_latent_attention_mma(_ptr(q_lat), _ptr(lane.k), _ptr(out), _ptr(scratch), _ptr(ctx.positions),
+                                                    _ptr(ctx.token_seq), _ptr(ctx.slot_dev), _ptr(lane.page_table),
+                                                    lane.page_table.shape[1], int(window), n, H, R, float(scale), n_splits,
+                                                    self._stream()), f"latent attention on tensor cores (rank {R}, {H} heads)")
+            if n_splits > 1:
+                LAUNCHES_EXTRA[0] += 1
+            return out
         check(self.lib.cpm_latent_attention(_ptr(q_lat), _ptr(lane.k), _ptr(out), _ptr(ctx.positions), _ptr(ctx.token_seq),
                                             _ptr(ctx.slot_dev), _ptr(lane.page_table), lane.page_table.shape[1], int(window),
                                             n, H, R, float(scale), self.code, self._stream()),
