@@ -514,6 +514,223 @@ def kernel_bench(name: str, batch: int, ctx: int, rows: int, n: int, k: int, rep
     return 0
 
 
+# Reravik at sizes that resemble a real model's layers: eight layers (attention over a cached latent, two gated
+# recurrences, attention, ...), the middle four run twice; random weights N(0, 0.02), vectors 1 + N(0, 0.02).
+RERAVIK_SIZES = {
+    "1k": dict(width=1024, ff=4096, heads=16, dim=64, vdim=64, q_rank=384, kv_rank=256, window=1024, vocab=32000),
+    "2k": dict(width=2048, ff=8192, heads=16, dim=128, vdim=128, q_rank=768, kv_rank=512, window=2048, vocab=32000),
+    "4k": dict(width=4096, ff=16384, heads=32, dim=128, vdim=128, q_rank=1536, kv_rank=512, window=4096, vocab=73448),
+}
+
+
+def reravik_config(z: dict) -> dict:
+    att = {"type": "latent_attention", "mlp": {"kind": "dense", "ff": z["ff"]},
+           "mixer": {"heads": z["heads"], "dim": z["dim"], "vdim": z["vdim"], "q_rank": z["q_rank"], "kv_rank": z["kv_rank"],
+                     "scale": z["dim"] ** -0.5, "mask": {"size": z["window"]}}}
+    gru = {"type": "mingru", "mixer": {"width": z["width"]}, "mlp": {"kind": "dense", "ff": z["ff"]}}
+    return {"architecture": "Reravik", "vocab": z["vocab"], "width": z["width"], "embedding": {"scale": 12.0},
+            "norm": {"eps": 1e-5}, "layers": [att, gru, gru, att, att, gru, gru, att], "loop": {"start": 2, "stop": 6, "times": 2}}
+
+
+def build_reravik(z: dict, max_tokens: int, max_batch: int, context: int):
+    import torch
+    from cpmcu_b200.engine import Stepper
+    from cpmcu_b200.engine.storage import make_storage
+    from cpmcu_b200.loading import build_model
+    from cpmcu_b200.registry import architecture
+    from cpmcu_b200.weights import random_tensors
+
+    arch = architecture("Reravik")
+    cfg = arch.config_class.from_dict(reravik_config(z))
+    model = build_model(arch, cfg, torch.bfloat16, "cuda:0")
+    storage = make_storage(model, PREFILL_TOKENS, max_batch, max_tokens=max_tokens, max_seq_tokens=context + 64, n_slots=max_batch + 2)
+    model.load_weights(random_tensors(model.weight_specs(), 4, torch.bfloat16, std=0.02, norm_mean=1.0, device="cuda:0"))
+    torch.cuda.empty_cache()
+    return cfg, model, storage.cache, Stepper(model, storage.cache, chunk_tokens=PREFILL_TOKENS, graph_prompts=True)
+
+
+def time_prefill_any(stepper, vocab: int, reps: int = 3) -> float:
+    import torch
+    from cpmcu_b200.engine import SequenceStep
+
+    times = []
+    for r in range(reps + 1):
+        ids = random_prompt(vocab, PREFILL_TOKENS, 500 + r)
+        slot = stepper.open(1)[0]
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        stepper.step([SequenceStep(slot, ids, [PREFILL_TOKENS - 1])])
+        e1.record()
+        torch.cuda.synchronize()
+        if r > 0:
+            times.append(e0.elapsed_time(e1))
+        stepper.close(slot)
+    return statistics.median(times)
+
+
+def reravik_kernels(z: dict, pk: dict, context: int, batch: int) -> dict:
+    """Every kernel of the design alone, at the size's shapes, beside the like kernel of the dense model: a prompt of
+    2,048 tokens and a decode step of ``batch`` sequences at ``context`` tokens.  CUDA events around one launch after
+    a flush of L2 (a 512 MB buffer is written), median of five; bytes and FLOPs are the algorithmic ones."""
+    import torch
+    from cpmcu_b200.cache import Cache
+    from cpmcu_b200.ops.ops import Ops
+    from cpmcu_b200.parts.base import CacheNeeds, QUERY_TILE_TOKENS, StepContext
+
+    ops = Ops(torch.bfloat16)
+    dev = "cuda:0"
+    flush = torch.empty(512 << 20, dtype=torch.uint8, device=dev)
+    W, H, R, QR, d, vd, win = z["width"], z["heads"], z["kv_rank"], z["q_rank"], z["dim"], z["vdim"], z["window"]
+    T = PREFILL_TOKENS
+    i32 = dict(dtype=torch.int32, device=dev)
+
+    def timed(fn):
+        ts = []
+        for _ in range(6):
+            flush.fill_(1)
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            ts.append(e0.elapsed_time(e1))
+        return statistics.median(ts[1:])
+
+    def context_of(q_lens, starts, slots):
+        pos = torch.cat([torch.arange(s, s + n) for n, s in zip(q_lens, starts)]).to(**i32)
+        seq = torch.cat([torch.full((n,), i) for i, n in enumerate(q_lens)]).to(**i32)
+        cu = torch.tensor([0] + [sum(q_lens[:i + 1]) for i in range(len(q_lens))], **i32)
+        kv = [s + n for n, s in zip(q_lens, starts)]
+        ctx = StepContext(n_tokens=sum(q_lens), n_seqs=len(q_lens), is_decode=all(n == 1 for n in q_lens), captured=False,
+                          q_lens=list(q_lens), kv_lens=kv, slots=list(slots), max_q_len=max(q_lens), max_kv_len=max(kv),
+                          token_ids=torch.zeros(sum(q_lens), **i32), positions=pos, token_seq=seq, cu_q=cu,
+                          kv_len_dev=torch.tensor(kv, **i32), slot_dev=torch.tensor(list(slots), **i32))
+        ts = [i for i, n in enumerate(q_lens) for _ in range(0, n, QUERY_TILE_TOKENS)]
+        tr = [r for n in q_lens for r in range(0, n, QUERY_TILE_TOKENS)]
+        ctx.q_tiles = (torch.tensor(ts, **i32), torch.tensor(tr, **i32), len(ts))
+        return ctx
+
+    out = {}
+
+    def note(name, ms, nbytes=0.0, flops=0.0, like=None):
+        row = {"us": ms * 1e3}
+        if nbytes:
+            row["gbs"] = nbytes / (ms * 1e-3) / 1e9
+            row["frac_hbm"] = row["gbs"] / pk["hbm_gbs"]
+        if flops:
+            row["tflops"] = flops / (ms * 1e-3) / 1e12
+            row["frac_bf16"] = row["tflops"] / pk["bf16_tflops"]
+        if like:
+            row["like"] = like
+        out[name] = row
+
+    n_slots = batch + 2
+    # latent lanes and dense lanes for the two designs' attention
+    latent = Cache([CacheNeeds(kv_heads=1, head_dim=R, values=False)], max_tokens=(batch + 1) * (context + 64), dtype=torch.bfloat16,
+                   device=dev, n_slots=n_slots)
+    dense = Cache([CacheNeeds(kv_heads=2, head_dim=d)], max_tokens=(batch + 1) * (context + 64), dtype=torch.bfloat16, device=dev,
+                  n_slots=n_slots)
+    slots = []
+    for c in (latent, dense):
+        slots = [c.open_sequence() for _ in range(batch)]
+        for s_ in slots:
+            c.reserve(s_, context)
+        c.sync()
+        c.lane(0).k.normal_(0, 0.5)
+        if c.lane(0).v is not None:
+            c.lane(0).v.normal_(0, 0.5)
+    for phase, q_lens, starts in (("prefill", [T], [0]), ("decode", [1] * batch, [context - 1] * batch)):
+        ctx = context_of(q_lens, starts, slots[:len(q_lens)])
+        n = ctx.n_tokens
+        x = torch.randn(n, W, device=dev)
+        a = torch.randn(n, W, device=dev).bfloat16()
+        vec = [torch.randn(W, device=dev) for _ in range(5)]
+        state = torch.zeros(n_slots, W, device=dev)
+        note(f"{phase}/layernorm_shift", timed(lambda: ops.layernorm_shift(ctx, x, vec[0], vec[1], 1e-5, vec[2], state)), n * W * 6.0,
+             like="add_rmsnorm")
+        note(f"{phase}/post_norm_add+norm", timed(lambda: ops.post_norm_add(x, a, vec[0], vec[1], 1e-5, (vec[2], vec[3]))), n * W * 12.0,
+             like="add_rmsnorm")
+        wn = torch.ones(W, device=dev)
+        note(f"{phase}/add_rmsnorm (dense model)", timed(lambda: ops.add_rmsnorm(x, a, 1.0, wn, 1e-5)), n * W * 12.0)
+        proj = torch.randn(n, 3 * W, device=dev)
+        gstate = torch.zeros(n_slots, W, device=dev)
+        note(f"{phase}/mingru_scan", timed(lambda: ops.mingru_scan(ctx, proj, vec[0], vec[1], gstate, W)), n * W * 14.0)
+        down = torch.randn(n, QR + R, device=dev)
+        gq, gkv = torch.ones(QR, device=dev), torch.ones(R, device=dev)
+        note(f"{phase}/latent_norm_store", timed(lambda: ops.latent_norm_store(ctx, down, gq, gkv, latent.lane(0), QR, R, 1e-5)),
+             n * (QR + R) * 6.0, like="rope_store")
+        qkv = torch.randn(n, (H + 4) * d, device=dev).bfloat16()
+        inv = torch.ones(d // 2, device=dev)
+        dl = dense.lane(0)
+        note(f"{phase}/rope_store (dense model)",
+             timed(lambda: ops.rope_store(qkv, H, 2, d, ctx.positions, ctx.token_seq, ctx.slot_dev, dl.page_table, dl.k, dl.v, inv, 1.0, d)),
+             n * (H + 4) * d * 2.0 + n * H * d * 2.0 + n * 4 * d * 2.0)
+        q = torch.randn(n, H * d, device=dev).bfloat16()
+        w_uk = torch.randn(H, d, R, device=dev).bfloat16()
+        w_uv = torch.randn(H, R, vd, device=dev).bfloat16()
+        note(f"{phase}/head_project q->latent", timed(lambda: ops.head_project(q, w_uk, H, out_f32=True)),
+             nbytes=n * H * (d * 2.0 + R * 4.0) + H * d * R * 2.0, flops=2.0 * n * H * d * R)
+        q_lat = ops.head_project(q, w_uk, H, out_f32=True)
+        keys = [min(win, s + j + 1) for nq, s in zip(q_lens, starts) for j in range(nq)]
+        note(f"{phase}/latent_attention", timed(lambda: ops.latent_attention(ctx, q_lat, latent.lane(0), d ** -0.5, win)),
+             nbytes=(sum(min(win, s + nq) for nq, s in zip(q_lens, starts)) * R * 2.0 + n * H * R * 8.0) if phase == "decode" else 0.0,
+             flops=4.0 * H * R * sum(keys), like="attention")
+        o_lat = ops.latent_attention(ctx, q_lat, latent.lane(0), d ** -0.5, win)
+        note(f"{phase}/head_project latent->values", timed(lambda: ops.head_project(o_lat, w_uv, H, out_f32=False)),
+             nbytes=n * H * (R * 4.0 + vd * 2.0) + H * vd * R * 2.0, flops=2.0 * n * H * vd * R)
+        qd = torch.randn(n, H, d, device=dev).bfloat16()
+        all_keys = [s + j + 1 for nq, s in zip(q_lens, starts) for j in range(nq)]
+        note(f"{phase}/attention (dense model, 2 kv heads, no window)", timed(lambda: ops.attention(ctx, qd, dl, 2, d ** -0.5)),
+             nbytes=(sum(s + nq for nq, s in zip(q_lens, starts)) * 2 * 2 * d * 2.0) if phase == "decode" else 0.0,
+             flops=4.0 * H * d * sum(all_keys))
+    return out
+
+
+def workload_reravik(steps: int, warmup: int, size: str, batch: int) -> int:
+    """Reravik at one of RERAVIK_SIZES beside MiniCPM4 with equal hidden size, feed-forward size, heads and as many
+    layers as the Reravik schedule has runs: decode steps of ``batch`` sequences ending at a context of 4,096 tokens
+    under a CUDA graph, a prompt of 2,048 tokens, and every kernel of the design alone beside its like."""
+    import torch
+
+    z, pk, context = RERAVIK_SIZES[size], peaks(), CONTEXT
+    cfg, model, cache, stepper = build_reravik(z, batch * (context + 64) + 128, batch, context)
+    runs = len(model.schedule)
+    pre_ms = time_prefill_any(stepper, cfg.vocab)
+    ms, clocks, launches, cache_bytes = time_decode(stepper, batch, steps, warmup, cfg.vocab, True, context=context)
+    weight_bytes = model.weight_bytes_per_step()
+    achieved = (weight_bytes + cache_bytes) / (ms * 1e-3) / 1e9
+    del model, cache, stepper
+    torch.cuda.empty_cache()
+    like = dict(MODEL, hidden_size=z["width"], intermediate_size=z["ff"], num_attention_heads=z["heads"], num_key_value_heads=2,
+                head_dim=z["dim"], vocab_size=z["vocab"])
+    dcfg, dmodel, dcache, dstepper = build_engine(runs, batch * (context + 64) + 128, batch, model=like, max_seq_tokens=context + 64)
+    d_pre = time_prefill_any(dstepper, dcfg.vocab_size)
+    d_ms, _, d_launches, d_cache = time_decode(dstepper, batch, steps, warmup, dcfg.vocab_size, False, context=context)
+    d_weights = dmodel.weight_bytes_per_step()
+    d_achieved = (d_weights + d_cache) / (d_ms * 1e-3) / 1e9
+    del dmodel, dcache, dstepper
+    torch.cuda.empty_cache()
+    kernels = reravik_kernels(z, pk, context, batch)
+    print(json.dumps({
+        "workload": "reravik", "metric": f"decode tokens/s (Reravik {size} sizes, bf16, batch {batch}, context {context})",
+        "value": batch * 1000.0 / ms, "unit": "tokens/s", "ms_per_step": ms, "steps": steps, "warmup": warmup, "dtype": "bf16",
+        "data": "synthetic: uniform-random token ids, random weights N(0,0.02) seed 4",
+        "config": dict(z, size=size, layers=len(cfg.layers), runs=runs, global_batch=batch, seq_len=context,
+                       prefill_tokens=PREFILL_TOKENS, cuda_graph=True, peaks=pk["source"]),
+        "prefill": {"value": PREFILL_TOKENS / (pre_ms * 1e-3), "ms": pre_ms},
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": achieved / pk["hbm_gbs"],
+                     "weight_bytes": weight_bytes, "cache_bytes": cache_bytes},
+        "closest_model": {"model": f"MiniCPM4 with hidden {z['width']}, intermediate {z['ff']}, {z['heads']} heads of {z['dim']}, 2 kv heads, {runs} layers",
+                          "decode_tokens_s": batch * 1000.0 / d_ms, "ms_per_step": d_ms, "prefill_tokens_s": PREFILL_TOKENS / (d_pre * 1e-3),
+                          "prefill_ms": d_pre, "roofline_frac": d_achieved / pk["hbm_gbs"], "weight_bytes": d_weights,
+                          "cache_bytes": d_cache, "gpu_launches": d_launches},
+        "kernels": kernels, "clocks": clocks, "gpu_launches": launches,
+    }))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -522,10 +739,12 @@ def main() -> int:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=FULL_LAYERS, help="layers built (the full model has 32)")
     ap.add_argument("--batch", type=int, default=8)
-    ap.add_argument("--workload", default="dense8b", choices=["dense8b", "half_b", "sparse8b"],
+    ap.add_argument("--workload", default="dense8b", choices=["dense8b", "half_b", "sparse8b", "reravik"],
                     help="dense8b: the headline line (8B sizes, batch 8, context 4096); half_b: 0.5B sizes, batch 64, prompts "
                          "uniform in [64, 2048] chunked at 512, decode at context 8192 (256 steps by default); sparse8b: 8B "
-                         "sizes with InfLLM-v2, prompts of 16384 and 30000 tokens chunked at 2048, then decode steps")
+                         "sizes with InfLLM-v2, prompts of 16384 and 30000 tokens chunked at 2048, then decode steps; reravik: the Reravik "
+                         "design at --size beside MiniCPM4 of equal sizes, and its kernels alone")
+    ap.add_argument("--size", default="2k", choices=sorted(RERAVIK_SIZES), help="--workload reravik: which layer sizes")
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 points and the e2e run")
     ap.add_argument("--kernel", default=None, help="time one kernel alone: skinny_gemm, decode_attention, prefill_attention (tcgen05), prefill_attention_mma, gemm_tcgen05; or run eager steps of a 2-layer model for a launch list: decode_step, prefill_step")
     ap.add_argument("--ctx", type=int, default=CONTEXT, help="--kernel: cached tokens per sequence (or prompt tokens)")
@@ -545,6 +764,8 @@ def main() -> int:
         return workload_half_b(a.steps if a.steps != 128 else 256, max(3, a.warmup))
     if a.workload == "sparse8b":
         return workload_sparse8b(a.steps, a.warmup, a.layers)
+    if a.workload == "reravik":
+        return workload_reravik(a.steps, max(3, a.warmup), a.size, a.batch)
     if a.kernel:
         return kernel_bench(a.kernel, a.batch, a.ctx, a.rows, a.n, a.k, a.reps)
     a.warmup = max(3, a.warmup)

@@ -62,47 +62,72 @@ CPM_API int cpm_latent_norm_store(const float* proj, const float* wq, const floa
 
 // ---------------------------------------------------------------------------
 constexpr int kProjectTokens = 8;      // tokens of one head that share a pass over the head's matrix
+constexpr int kProjectCols = 32;       // output columns of a block
+constexpr int kProjectParts = 8;       // parts of the sum over k, one per warp
 
+// A block is 8 tokens x one head x 32 output columns; its eight warps split the sum over k (a warp reads 32
+// consecutive columns of every eighth row of the head's matrix, four rows in flight) and add up through shared memory.
 template <typename In, typename Wt, typename Out>
-__global__ void head_project_kernel(const In* __restrict__ in, const Wt* __restrict__ w, Out* __restrict__ out,
-                                    int n_tokens, int n_heads, int K, int N) {
-    extern __shared__ float hp_smem[];      // [kProjectTokens][K]
+__global__ void __launch_bounds__(kProjectCols * kProjectParts)
+head_project_kernel(const In* __restrict__ in, const Wt* __restrict__ w, Out* __restrict__ out,
+                    int n_tokens, int n_heads, int K, int N) {
+    extern __shared__ float hp_smem[];      // [kProjectTokens][K] inputs, then [parts][tokens][cols] partial sums
+    float* part = hp_smem + kProjectTokens * K;
     pdl_launch_dependents();
     pdl_wait();
     const int h = blockIdx.y;
     const int t0 = blockIdx.x * kProjectTokens;
     const int nt = min(kProjectTokens, n_tokens - t0);
-    for (int i = threadIdx.x; i < nt * K; i += blockDim.x) {
+    for (int i = threadIdx.x; i < kProjectTokens * K; i += blockDim.x) {
         const int tt = i / K, k = i % K;
-        hp_smem[tt * K + k] = to_f32(in[((int64_t)(t0 + tt) * n_heads + h) * K + k]);
+        hp_smem[i] = tt < nt ? to_f32(in[((int64_t)(t0 + tt) * n_heads + h) * K + k]) : 0.f;
     }
     __syncthreads();
-    const Wt* wh = w + (int64_t)h * K * N;
-    for (int n = threadIdx.x; n < N; n += blockDim.x) {
-        float acc[kProjectTokens];
+    const int col = threadIdx.x % kProjectCols, kp = threadIdx.x / kProjectCols;
+    const int n = blockIdx.z * kProjectCols + col;
+    const Wt* wh = w + (int64_t)h * K * N + (n < N ? n : 0);
+    float acc[kProjectTokens];
 #pragma unroll
-        for (int tt = 0; tt < kProjectTokens; ++tt) acc[tt] = 0.f;
-        for (int k = 0; k < K; ++k) {
-            const float wv = to_f32(wh[(int64_t)k * N + n]);
+    for (int tt = 0; tt < kProjectTokens; ++tt) acc[tt] = 0.f;
+    int k = kp;
+    for (; k + 3 * kProjectParts < K; k += 4 * kProjectParts) {
+        float wv[4];
 #pragma unroll
-            for (int tt = 0; tt < kProjectTokens; ++tt) acc[tt] = fmaf(hp_smem[tt * K + k], wv, acc[tt]);
-        }
-        for (int tt = 0; tt < nt; ++tt) out[((int64_t)(t0 + tt) * n_heads + h) * N + n] = from_f32<Out>(acc[tt]);
+        for (int u = 0; u < 4; ++u) wv[u] = to_f32(wh[(int64_t)(k + u * kProjectParts) * N]);
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+#pragma unroll
+            for (int tt = 0; tt < kProjectTokens; ++tt) acc[tt] = fmaf(hp_smem[tt * K + k + u * kProjectParts], wv[u], acc[tt]);
+    }
+    for (; k < K; k += kProjectParts) {
+        const float wv = to_f32(wh[(int64_t)k * N]);
+#pragma unroll
+        for (int tt = 0; tt < kProjectTokens; ++tt) acc[tt] = fmaf(hp_smem[tt * K + k], wv, acc[tt]);
+    }
+#pragma unroll
+    for (int tt = 0; tt < kProjectTokens; ++tt) part[(kp * kProjectTokens + tt) * kProjectCols + col] = acc[tt];
+    __syncthreads();
+    const int tt = threadIdx.x / kProjectCols;            // 8 tokens x 32 columns = the block's 256 threads
+    if (tt < nt && n < N) {
+        float sum = 0.f;
+#pragma unroll
+        for (int p = 0; p < kProjectParts; ++p) sum += part[(p * kProjectTokens + tt) * kProjectCols + col];
+        out[((int64_t)(t0 + tt) * n_heads + h) * N + n] = from_f32<Out>(sum);
     }
 }
 
 template <typename In, typename Wt, typename Out>
 static int launch_head_project(const void* in, const void* w, void* out, int n_tokens, int n_heads, int K, int N,
                                cudaStream_t stream) {
-    const size_t smem = (size_t)kProjectTokens * K * sizeof(float);
+    const size_t smem = (size_t)kProjectTokens * (K + kProjectParts * kProjectCols) * sizeof(float);
     auto kern = head_project_kernel<In, Wt, Out>;
     if (smem > 227 * 1024) return CPM_BAD_ARGUMENT;
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
     }
-    dim3 grid((n_tokens + kProjectTokens - 1) / kProjectTokens, n_heads);
-    const int threads = N >= 256 ? 256 : (N >= 128 ? 128 : 64);
+    dim3 grid((n_tokens + kProjectTokens - 1) / kProjectTokens, n_heads, (N + kProjectCols - 1) / kProjectCols);
+    const int threads = kProjectCols * kProjectParts;
     cpm_launch(kLaunchProduct, kern, grid, threads, smem, stream, (const In*)in, (const Wt*)w, (Out*)out, n_tokens, n_heads, K, N);
     return launch_status();
 }
@@ -112,7 +137,7 @@ static int launch_head_project(const void* in, const void* w, void* out, int n_t
 CPM_API int cpm_head_project(const void* in, const void* w, void* out, int n_tokens, int n_heads, int K, int N, int in_f32,
                              int out_f32, int dtype, cudaStream_t stream) {
     if (n_tokens <= 0) return CPM_OK;
-    if (n_heads <= 0 || n_heads > 65535 || K <= 0 || N <= 0) return CPM_BAD_ARGUMENT;
+    if (n_heads <= 0 || n_heads > 65535 || K <= 0 || N <= 0 || (N + kProjectCols - 1) / kProjectCols > 65535) return CPM_BAD_ARGUMENT;
     if (dtype == CPM_F32) return launch_head_project<float, float, float>(in, w, out, n_tokens, n_heads, K, N, stream);
     if (in_f32 && out_f32) return launch_head_project<float, bf16, float>(in, w, out, n_tokens, n_heads, K, N, stream);
     if (in_f32) return launch_head_project<float, bf16, bf16>(in, w, out, n_tokens, n_heads, K, N, stream);
@@ -258,18 +283,34 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     return *reinterpret_cast<const uint32_t*>(&v);
 }
 
-// NT: column groups of 8 a warp may own (rank <= 32 * NT).  scratch per (token, head group, share): 16 * (rank + 2) floats.
+constexpr int kPageSlots = 1024;      // page numbers of a block's keys kept in shared memory (beyond: read from the table)
+
+__device__ __forceinline__ void cp_async_16(void* smem, const void* gmem, bool real) {
+    const uint32_t dst = (uint32_t)__cvta_generic_to_shared(smem);
+    const int bytes = real ? 16 : 0;                                     // 0: the 16 bytes are filled with zeros
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(gmem), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// NT: column groups of 8 a warp may own in the weighted sum (rank <= 32 * NT); the same number bounds the 16-wide steps
+// of the rank a warp owns in the scores (rank / 64, rounded up, <= NT / 2).  Per tile of 32 latent rows: the four warps
+// split the rank for the scores (each keeps its part of the 16 query rows in registers for the whole kernel and leaves a
+// partial 16 x 32 score tile in shared memory), every warp adds the four partials and keeps the softmax statistics, and
+// the warps split the latent columns for the weighted sum.  Tiles arrive by cp.async one tile ahead, in two buffers.
+// scratch per (token, head group, share): 16 * (rank + 2) floats.
 template <int NT>
 __global__ void __launch_bounds__(128)
-latent_attention_mma_kernel(const float* __restrict__ q, const bf16* __restrict__ cache, float* __restrict__ out,
+latent_attention_mma_kernel(const float* __restrict__ q, const bf16* __restrict__ cache, void* __restrict__ out_any, int out_bf16,
                             float* __restrict__ scratch, const int* __restrict__ positions, const int* __restrict__ token_seq,
                             const int* __restrict__ slots, const int* __restrict__ page_table, int max_pages, int window,
                             int n_heads, int rank, float scale, int n_splits) {
+    constexpr int KS = NT / 2;                                           // 16-wide steps of the rank per warp, at most
     extern __shared__ __align__(16) unsigned char lm_smem[];
-    const int pitch = rank + 8;                                          // bf16 elements per row of Qs and Ks
-    bf16* Qs = reinterpret_cast<bf16*>(lm_smem);                         // [16][pitch]
-    bf16* Ks = Qs + kMmaRows * pitch;                                    // [32][pitch]
-    float* Ss = reinterpret_cast<float*>(Ks + kMmaKeys * pitch);         // [16][33]
+    __shared__ int page_s[kPageSlots];
+    const int pitch = rank + 8;                                          // bf16 elements per latent row in shared memory
+    bf16* Ks = reinterpret_cast<bf16*>(lm_smem);                         // [2][32][pitch]
+    float* Ss = reinterpret_cast<float*>(Ks + 2 * kMmaKeys * pitch);     // [4 warps][16][33]
     pdl_launch_dependents();
     pdl_wait();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, tg = lane & 3;
@@ -280,53 +321,90 @@ latent_attention_mma_kernel(const float* __restrict__ q, const bf16* __restrict_
     const int tiles_total = (p + 1 - lo + kMmaKeys - 1) / kMmaKeys;
     const int per = (tiles_total + n_splits - 1) / n_splits;
     const int tile0 = split * per, tile1 = min(tiles_total, tile0 + per);
+    const int k_steps = rank / 16;
 
-    for (int i = threadIdx.x; i < kMmaRows * rank; i += blockDim.x) {
-        const int r = i / rank, c = i % rank;
-        const int h = h0 + r;
-        Qs[r * pitch + c] = __float2bfloat16_rn(h < n_heads ? q[((int64_t)t * n_heads + h) * rank + c] : 0.f);
+    // this warp's part of the queries, as A fragments: 16-wide steps warp, warp + 4, ... of the rank
+    uint32_t qa[KS][4];
+#pragma unroll
+    for (int i = 0; i < KS; ++i) {
+        const int ks = warp + 4 * i;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int h = h0 + g + 8 * (e & 1);
+            const int c = ks * 16 + 2 * tg + 8 * (e >> 1);
+            float2 v = make_float2(0.f, 0.f);
+            if (ks < k_steps && h < n_heads) v = *reinterpret_cast<const float2*>(q + ((int64_t)t * n_heads + h) * rank + c);
+            qa[i][e] = pack_bf16(v.x, v.y);
+        }
     }
+    const int first_page = (lo + tile0 * kMmaKeys) / kPageTokens;
+    const int last_key = min(p, lo + tile1 * kMmaKeys - 1);
+    const int n_block_pages = tile1 > tile0 ? last_key / kPageTokens - first_page + 1 : 0;
+    const bool pages_in_smem = n_block_pages <= kPageSlots;
+    if (pages_in_smem)
+        for (int i = threadIdx.x; i < n_block_pages; i += blockDim.x) page_s[i] = CPM_PAGE(pages, first_page + i, max_pages);
+    __syncthreads();
+
+    const int vec_per_row = rank / 8;                                    // 16-byte pieces of a latent row
+    auto fetch = [&](int tile, int buf) {
+        const int j0 = lo + tile * kMmaKeys;
+        bf16* dst = Ks + buf * kMmaKeys * pitch;
+        for (int i = threadIdx.x; i < kMmaKeys * vec_per_row; i += blockDim.x) {
+            const int r = i / vec_per_row, v = i % vec_per_row;
+            const int j = j0 + r;
+            const bool real = j <= p;
+            const bf16* src = cache;
+            if (real) {
+                const int lp = j / kPageTokens;
+                const int page = pages_in_smem ? page_s[lp - first_page] : CPM_PAGE(pages, lp, max_pages);
+                src = cache + page_row_offset(page, 0, j % kPageTokens, 1, rank) + 8 * v;
+            }
+            cp_async_16(dst + r * pitch + 8 * v, src, real);
+        }
+        cp_async_commit();
+    };
+
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};             // rows g and g + 8
     float acc[NT][4];
 #pragma unroll
     for (int i = 0; i < NT; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
-    const int k_steps = rank / 16;
-    const int vec_per_row = rank / 8;                                    // 16-byte pieces of a latent row
 
+    if (tile0 < tile1) fetch(tile0, 0);
     for (int tile = tile0; tile < tile1; ++tile) {
+        const int buf = (tile - tile0) & 1;
         const int j0 = lo + tile * kMmaKeys;
-        __syncthreads();                                                 // Ks, Ss of the tile before are no longer read
-        for (int i = threadIdx.x; i < kMmaKeys * vec_per_row; i += blockDim.x) {
-            const int r = i / vec_per_row, v = i % vec_per_row;
-            const int j = j0 + r;
-            uint4 val = make_uint4(0u, 0u, 0u, 0u);
-            if (j <= p) {
-                const int page = CPM_PAGE(pages, j / kPageTokens, max_pages);
-                val = *reinterpret_cast<const uint4*>(cache + page_row_offset(page, 0, j % kPageTokens, 1, rank) + 8 * v);
-            }
-            *reinterpret_cast<uint4*>(Ks + r * pitch + 8 * v) = val;
+        if (tile + 1 < tile1) {
+            fetch(tile + 1, buf ^ 1);
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
         }
-        __syncthreads();
-        {   // scores of keys 8 * warp .. + 8 for all 16 rows
-            float c[4] = {0.f, 0.f, 0.f, 0.f};
-            const bf16* krow = Ks + (8 * warp + g) * pitch;
-            for (int ks = 0; ks < k_steps; ++ks) {
-                uint32_t a[4];
-                const bf16* q0 = Qs + g * pitch + ks * 16 + 2 * tg;
-                a[0] = *reinterpret_cast<const uint32_t*>(q0);
-                a[1] = *reinterpret_cast<const uint32_t*>(q0 + 8 * pitch);
-                a[2] = *reinterpret_cast<const uint32_t*>(q0 + 8);
-                a[3] = *reinterpret_cast<const uint32_t*>(q0 + 8 * pitch + 8);
-                const uint32_t b0 = *reinterpret_cast<const uint32_t*>(krow + ks * 16 + 2 * tg);
-                const uint32_t b1 = *reinterpret_cast<const uint32_t*>(krow + ks * 16 + 8 + 2 * tg);
-                mma_bf16_16816(c, a, b0, b1);
+        __syncthreads();                                                 // the tile is there for every warp
+        const bf16* Kt = Ks + buf * kMmaKeys * pitch;
+        {   // partial scores of all 32 keys over this warp's part of the rank
+            float c[4][4];
+#pragma unroll
+            for (int n = 0; n < 4; ++n) c[n][0] = c[n][1] = c[n][2] = c[n][3] = 0.f;
+#pragma unroll
+            for (int i = 0; i < KS; ++i) {
+                const int ks = warp + 4 * i;
+                if (ks < k_steps) {
+#pragma unroll
+                    for (int n = 0; n < 4; ++n) {
+                        const bf16* krow = Kt + (8 * n + g) * pitch + ks * 16 + 2 * tg;
+                        mma_bf16_16816(c[n], qa[i], *reinterpret_cast<const uint32_t*>(krow), *reinterpret_cast<const uint32_t*>(krow + 8));
+                    }
+                }
             }
-            const int col = 8 * warp + 2 * tg;
-            const bool ok0 = j0 + col <= p, ok1 = j0 + col + 1 <= p;
-            Ss[g * 33 + col] = ok0 ? c[0] * scale : -INFINITY;
-            Ss[g * 33 + col + 1] = ok1 ? c[1] * scale : -INFINITY;
-            Ss[(g + 8) * 33 + col] = ok0 ? c[2] * scale : -INFINITY;
-            Ss[(g + 8) * 33 + col + 1] = ok1 ? c[3] * scale : -INFINITY;
+            float* mine = Ss + warp * kMmaRows * 33;
+#pragma unroll
+            for (int n = 0; n < 4; ++n) {
+                const int col = 8 * n + 2 * tg;
+                mine[g * 33 + col] = c[n][0];
+                mine[g * 33 + col + 1] = c[n][1];
+                mine[(g + 8) * 33 + col] = c[n][2];
+                mine[(g + 8) * 33 + col + 1] = c[n][3];
+            }
         }
         __syncthreads();
         // softmax of the tile, kept by every warp alike; a thread holds, for rows g and g + 8, the columns
@@ -335,10 +413,14 @@ latent_attention_mma_kernel(const float* __restrict__ q, const bf16* __restrict_
 #pragma unroll
         for (int half = 0; half < 2; ++half)
 #pragma unroll
-            for (int r = 0; r < 2; ++r) {
-                const float* row = Ss + (g + 8 * r) * 33 + 16 * half + 2 * tg;
-                s[half][r][0] = row[0]; s[half][r][1] = row[1]; s[half][r][2] = row[8]; s[half][r][3] = row[9];
-            }
+            for (int r = 0; r < 2; ++r)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int col = 16 * half + 2 * tg + (e & 1) + 8 * (e >> 1);
+                    const float* cell = Ss + (g + 8 * r) * 33 + col;
+                    const float v = cell[0] + cell[kMmaRows * 33] + cell[2 * kMmaRows * 33] + cell[3 * kMmaRows * 33];
+                    s[half][r][e] = j0 + col <= p ? v * scale : -INFINITY;
+                }
         uint32_t pa[2][4];
 #pragma unroll
         for (int r = 0; r < 2; ++r) {
@@ -381,12 +463,13 @@ latent_attention_mma_kernel(const float* __restrict__ q, const bf16* __restrict_
 #pragma unroll
                 for (int half = 0; half < 2; ++half) {
                     uint32_t b0, b1;
-                    const uint32_t addr = (uint32_t)__cvta_generic_to_shared(Ks + (16 * half + (lane & 15)) * pitch + col0);
+                    const uint32_t addr = (uint32_t)__cvta_generic_to_shared(Kt + (16 * half + (lane & 15)) * pitch + col0);
                     asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];" : "=r"(b0), "=r"(b1) : "r"(addr));
                     mma_bf16_16816(acc[i], pa[half], b0, b1);
                 }
             }
         }
+        __syncthreads();                                                 // this buffer and the scores may be overwritten
     }
     // rows g and g + 8 are heads h0 + g and h0 + g + 8; a thread holds columns col0 + 2tg, + 1 of its column groups
     if (n_splits == 1) {
@@ -395,11 +478,13 @@ latent_attention_mma_kernel(const float* __restrict__ q, const bf16* __restrict_
             const int h = h0 + g + 8 * r;
             if (h >= n_heads) continue;
             const float inv = l[r] > 0.f ? 1.f / l[r] : 0.f;
-            float* orow = out + ((int64_t)t * n_heads + h) * rank;
+            const int64_t o = ((int64_t)t * n_heads + h) * rank;
 #pragma unroll
             for (int i = 0; i < NT; ++i) {
                 const int c = 8 * (warp + 4 * i) + 2 * tg;
-                if (c < rank) *reinterpret_cast<float2*>(orow + c) = make_float2(acc[i][2 * r] * inv, acc[i][2 * r + 1] * inv);
+                if (c >= rank) continue;
+                if (out_bf16) *reinterpret_cast<uint32_t*>(static_cast<bf16*>(out_any) + o + c) = pack_bf16(acc[i][2 * r] * inv, acc[i][2 * r + 1] * inv);
+                else *reinterpret_cast<float2*>(static_cast<float*>(out_any) + o + c) = make_float2(acc[i][2 * r] * inv, acc[i][2 * r + 1] * inv);
             }
         }
         return;
@@ -417,8 +502,8 @@ latent_attention_mma_kernel(const float* __restrict__ q, const bf16* __restrict_
     }
 }
 
-__global__ void latent_attention_merge_kernel(const float* __restrict__ scratch, float* __restrict__ out, int n_heads, int rank,
-                                              int n_splits) {
+__global__ void latent_attention_merge_kernel(const float* __restrict__ scratch, void* __restrict__ out_any, int out_bf16, int n_heads,
+                                              int rank, int n_splits) {
     pdl_launch_dependents();
     pdl_wait();
     const int t = blockIdx.x, hg = blockIdx.y;
@@ -436,7 +521,9 @@ __global__ void latent_attention_merge_kernel(const float* __restrict__ scratch,
             l = fmaf(prow[rank + 1], w, l);
             o = fmaf(prow[c], w, o);
         }
-        out[((int64_t)t * n_heads + h) * rank + c] = l > 0.f ? o / l : 0.f;
+        const float res = l > 0.f ? o / l : 0.f;
+        if (out_bf16) static_cast<bf16*>(out_any)[((int64_t)t * n_heads + h) * rank + c] = __float2bfloat16_rn(res);
+        else static_cast<float*>(out_any)[((int64_t)t * n_heads + h) * rank + c] = res;
     }
 }
 
@@ -446,37 +533,37 @@ CPM_API int64_t cpm_latent_attention_scratch_floats(int n_tokens, int n_heads, i
 }
 
 template <int NT>
-static int launch_latent_mma(const float* q, const void* cache, float* out, float* scratch, const int* positions,
+static int launch_latent_mma(const float* q, const void* cache, void* out, int out_bf16, float* scratch, const int* positions,
                              const int* token_seq, const int* slots, const int* page_table, int max_pages, int window,
                              int n_tokens, int n_heads, int rank, float scale, int n_splits, cudaStream_t stream) {
     static bool smem_done[kMaxDevices];
-    const size_t smem = (size_t)(kMmaRows + kMmaKeys) * (rank + 8) * sizeof(bf16) + (size_t)kMmaRows * 33 * sizeof(float);
+    const size_t smem = (size_t)2 * kMmaKeys * (rank + 8) * sizeof(bf16) + (size_t)4 * kMmaRows * 33 * sizeof(float);
     auto kern = latent_attention_mma_kernel<NT>;
     if (smem > 48 * 1024)
         if (int e = ensure_dynamic_smem(kern, (int)smem, smem_done)) return e;
     const int groups = (n_heads + kMmaRows - 1) / kMmaRows;
     dim3 grid(n_tokens, groups, n_splits);
-    cpm_launch(kLaunchAttention, kern, grid, 128, smem, stream, q, (const bf16*)cache, out, scratch, positions, token_seq, slots,
+    cpm_launch(kLaunchAttention, kern, grid, 128, smem, stream, q, (const bf16*)cache, out, out_bf16, scratch, positions, token_seq, slots,
                page_table, max_pages, window, n_heads, rank, scale, n_splits);
     if (n_splits > 1)
         cpm_launch(kLaunchCombine, latent_attention_merge_kernel, dim3(n_tokens, groups), 256, 0, stream, (const float*)scratch, out,
-                   n_heads, rank, n_splits);
+                   out_bf16, n_heads, rank, n_splits);
     return launch_status();
 }
 
-// bf16 latents, rank a multiple of 16 up to 512; ``scratch``: cpm_latent_attention_scratch_floats floats when n_splits > 1.
-CPM_API int cpm_latent_attention_mma(const float* q, const void* cache, float* out, float* scratch, const int* positions,
+// bf16 latents, rank a multiple of 16 up to 512; ``out`` fp32, or bf16 with ``out_bf16``; ``scratch``: cpm_latent_attention_scratch_floats floats when n_splits > 1.
+CPM_API int cpm_latent_attention_mma(const float* q, const void* cache, void* out, int out_bf16, float* scratch, const int* positions,
                                      const int* token_seq, const int* slots, const int* page_table, int max_pages, int window,
                                      int n_tokens, int n_heads, int rank, float scale, int n_splits, cudaStream_t stream) {
     if (n_tokens <= 0) return CPM_OK;
     if (n_heads <= 0 || rank <= 0 || rank > 512 || rank % 16 || window < 0 || n_splits < 1 || n_splits > 65535) return CPM_BAD_ARGUMENT;
     if (n_splits > 1 && scratch == nullptr) return CPM_BAD_ARGUMENT;
     if ((n_heads + kMmaRows - 1) / kMmaRows > 65535) return CPM_BAD_ARGUMENT;
-    if (rank <= 128) return launch_latent_mma<4>(q, cache, out, scratch, positions, token_seq, slots, page_table, max_pages, window,
+    if (rank <= 128) return launch_latent_mma<4>(q, cache, out, out_bf16, scratch, positions, token_seq, slots, page_table, max_pages, window,
                                                   n_tokens, n_heads, rank, scale, n_splits, stream);
-    if (rank <= 256) return launch_latent_mma<8>(q, cache, out, scratch, positions, token_seq, slots, page_table, max_pages, window,
+    if (rank <= 256) return launch_latent_mma<8>(q, cache, out, out_bf16, scratch, positions, token_seq, slots, page_table, max_pages, window,
                                                   n_tokens, n_heads, rank, scale, n_splits, stream);
-    return launch_latent_mma<16>(q, cache, out, scratch, positions, token_seq, slots, page_table, max_pages, window, n_tokens,
+    return launch_latent_mma<16>(q, cache, out, out_bf16, scratch, positions, token_seq, slots, page_table, max_pages, window, n_tokens,
                                  n_heads, rank, scale, n_splits, stream);
 }
 

@@ -11,25 +11,79 @@
 // the loads of ``a`` and the stores of ``y`` touch the storage type.  Weights, biases and mu are fp32.
 #include "common.cuh"
 
-// Loads one fp32 row into ``buf`` and leaves there its normed values.
+// Four consecutive elements as floats (16-byte or 8-byte aligned loads).
+__device__ __forceinline__ float4 ln_load4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 ln_load4(const bf16* p) {
+    const uint2 raw = *reinterpret_cast<const uint2*>(p);
+    const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+    const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+    return make_float4(lo.x, lo.y, hi.x, hi.y);
+}
+
+__device__ __forceinline__ void ln_store4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void ln_store4(bf16* p, float4 v) {
+    const __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+    uint2 raw;
+    raw.x = *reinterpret_cast<const uint32_t*>(&lo);
+    raw.y = *reinterpret_cast<const uint32_t*>(&hi);
+    *reinterpret_cast<uint2*>(p) = raw;
+}
+
+// Copies a normed row from shared memory to its place in the storage type.
+template <typename T>
+__device__ __forceinline__ void ln_write_row(T* __restrict__ dst, const float* buf, int hidden) {
+    if ((hidden & 3) == 0) {
+        for (int c = 4 * threadIdx.x; c < hidden; c += 4 * blockDim.x) ln_store4(dst + c, *reinterpret_cast<const float4*>(buf + c));
+    } else {
+        for (int c = threadIdx.x; c < hidden; c += blockDim.x) dst[c] = from_f32<T>(buf[c]);
+    }
+}
+
+// Loads one row into ``buf`` (fp32, 16-byte aligned; it may be the row itself) and leaves there its normed values.
 template <typename In>
-__device__ __forceinline__ void norm_row_into(const In* __restrict__ src, float* buf, const float* __restrict__ w,
+__device__ __forceinline__ void norm_row_into(const In* src, float* buf, const float* __restrict__ w,
                                               const float* __restrict__ b, int hidden, float eps, float* scratch) {
+    const bool wide = (hidden & 3) == 0;
     float s = 0.f;
-    for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
-        const float v = to_f32(src[c]);
-        buf[c] = v;
-        s += v;
+    if (wide) {
+        for (int c = 4 * threadIdx.x; c < hidden; c += 4 * blockDim.x) {
+            const float4 v = ln_load4(src + c);
+            *reinterpret_cast<float4*>(buf + c) = v;
+            s += (v.x + v.y) + (v.z + v.w);
+        }
+    } else {
+        for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+            const float v = to_f32(src[c]);
+            buf[c] = v;
+            s += v;
+        }
     }
     const float mean = block_sum(s, scratch) / (float)hidden;
     float q = 0.f;
-    for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
-        const float d = buf[c] - mean;
-        q = fmaf(d, d, q);
+    if (wide) {
+        for (int c = 4 * threadIdx.x; c < hidden; c += 4 * blockDim.x) {
+            const float4 v = *reinterpret_cast<const float4*>(buf + c);
+            const float d0 = v.x - mean, d1 = v.y - mean, d2 = v.z - mean, d3 = v.w - mean;
+            q = fmaf(d0, d0, fmaf(d1, d1, fmaf(d2, d2, fmaf(d3, d3, q))));
+        }
+    } else {
+        for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+            const float d = buf[c] - mean;
+            q = fmaf(d, d, q);
+        }
     }
     const float var = block_sum(q, scratch) / (float)hidden;
     const float r = 1.0f / sqrtf(var + eps);
-    for (int c = threadIdx.x; c < hidden; c += blockDim.x) buf[c] = (buf[c] - mean) * r * w[c] + b[c];
+    if (wide) {
+        for (int c = 4 * threadIdx.x; c < hidden; c += 4 * blockDim.x) {
+            const float4 v = *reinterpret_cast<const float4*>(buf + c);
+            const float4 w4 = *reinterpret_cast<const float4*>(w + c), b4 = *reinterpret_cast<const float4*>(b + c);
+            *reinterpret_cast<float4*>(buf + c) = make_float4((v.x - mean) * r * w4.x + b4.x, (v.y - mean) * r * w4.y + b4.y,
+                                                              (v.z - mean) * r * w4.z + b4.z, (v.w - mean) * r * w4.w + b4.w);
+        }
+    } else {
+        for (int c = threadIdx.x; c < hidden; c += blockDim.x) buf[c] = (buf[c] - mean) * r * w[c] + b[c];
+    }
 }
 
 template <typename T>
@@ -42,8 +96,8 @@ __global__ void layernorm_rows_kernel(const float* __restrict__ x, const float* 
     pdl_wait();
     const int64_t src = rows ? rows[blockIdx.x] : blockIdx.x;
     norm_row_into(x + src * hidden, buf, w, b, hidden, eps, scratch);
-    T* yr = y + (int64_t)blockIdx.x * hidden;
-    for (int c = threadIdx.x; c < hidden; c += blockDim.x) yr[c] = from_f32<T>(buf[c]);
+    __syncthreads();
+    ln_write_row(y + (int64_t)blockIdx.x * hidden, buf, hidden);
 }
 
 // One block per token.  The block of a sequence's first token of the step takes h_{t-1} from the sequence's
@@ -69,14 +123,25 @@ __global__ void layernorm_shift_kernel(const float* __restrict__ x, const float*
     if (first) {
         st = state + (int64_t)slots[seq] * hidden;
         const bool start = positions[t] == 0;
+        __syncthreads();                      // the state is read before this block writes it below
         for (int c = threadIdx.x; c < hidden; c += blockDim.x) prev[c] = start ? 0.f : st[c];
     } else {
         norm_row_into(x + (int64_t)(t - 1) * hidden, prev, w, b, hidden, eps, scratch);
     }
+    __syncthreads();
     T* yr = y + (int64_t)t * hidden;
-    for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
-        const float h = cur[c];
-        yr[c] = from_f32<T>(h + (prev[c] - h) * mu[c]);
+    if ((hidden & 3) == 0) {
+        for (int c = 4 * threadIdx.x; c < hidden; c += 4 * blockDim.x) {
+            const float4 h = *reinterpret_cast<const float4*>(cur + c), pv = *reinterpret_cast<const float4*>(prev + c);
+            const float4 m4 = *reinterpret_cast<const float4*>(mu + c);
+            ln_store4(yr + c, make_float4(h.x + (pv.x - h.x) * m4.x, h.y + (pv.y - h.y) * m4.y, h.z + (pv.z - h.z) * m4.z,
+                                          h.w + (pv.w - h.w) * m4.w));
+        }
+    } else {
+        for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+            const float h = cur[c];
+            yr[c] = from_f32<T>(h + (prev[c] - h) * mu[c]);
+        }
     }
     if (first) {
         const int last = cu_q[seq + 1] - 1;
@@ -85,6 +150,7 @@ __global__ void layernorm_shift_kernel(const float* __restrict__ x, const float*
         } else {
             __syncthreads();
             norm_row_into(x + (int64_t)last * hidden, prev, w, b, hidden, eps, scratch);
+            __syncthreads();
             for (int c = threadIdx.x; c < hidden; c += blockDim.x) st[c] = prev[c];
         }
     }
@@ -102,12 +168,27 @@ __global__ void post_norm_add_kernel(float* __restrict__ x, const T* __restrict_
     const int64_t t = blockIdx.x;
     norm_row_into(a + t * hidden, buf, w, b, hidden, eps, scratch);
     float* xr = x + t * hidden;
-    for (int c = threadIdx.x; c < hidden; c += blockDim.x) xr[c] += buf[c];
+    __syncthreads();
+    // the new stream goes to its place and stays in shared memory for the norm that follows
+    if ((hidden & 3) == 0) {
+        for (int c = 4 * threadIdx.x; c < hidden; c += 4 * blockDim.x) {
+            const float4 n = *reinterpret_cast<const float4*>(buf + c), old = *reinterpret_cast<const float4*>(xr + c);
+            const float4 v = make_float4(old.x + n.x, old.y + n.y, old.z + n.z, old.w + n.w);
+            *reinterpret_cast<float4*>(xr + c) = v;
+            *reinterpret_cast<float4*>(buf + c) = v;
+        }
+    } else {
+        for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+            const float v = xr[c] + buf[c];
+            xr[c] = v;
+            buf[c] = v;
+        }
+    }
     if (w2 == nullptr) return;
     __syncthreads();
-    norm_row_into(xr, buf, w2, b2, hidden, eps, scratch);      // every thread reads back what it wrote itself
-    T* yr = y + t * hidden;
-    for (int c = threadIdx.x; c < hidden; c += blockDim.x) yr[c] = from_f32<T>(buf[c]);
+    norm_row_into(buf, buf, w2, b2, hidden, eps, scratch);
+    __syncthreads();
+    ln_write_row(y + t * hidden, buf, hidden);
 }
 
 __global__ void stream_inject_kernel(float* __restrict__ x, const float* __restrict__ saved, const float* __restrict__ vec,

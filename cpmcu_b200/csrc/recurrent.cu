@@ -19,6 +19,8 @@
 
 __device__ __forceinline__ float sigmoid_f32(float v) { return 1.0f / (1.0f + expf(-v)); }
 
+constexpr int kGruBatch = 8;      // tokens whose projections are loaded before the first is used
+
 struct GruStep { float a, b; };      // S <- a * S + b
 
 __device__ __forceinline__ GruStep mingru_gates(float zr, float ur) {
@@ -42,12 +44,23 @@ __global__ void mingru_scan_seq_kernel(const float* __restrict__ proj, const flo
     float* st = state + (int64_t)slots[seq] * width + c;
     float S = positions[t0] == 0 ? 0.f : *st;
     const float bzc = bz[c], bxc = bx[c];
-    for (int t = t0; t < t1; ++t) {
-        const float* row = proj + (int64_t)t * 3 * width;
-        const GruStep g = mingru_gates(row[c] + bzc, row[width + c] + bxc);
-        S = fmaf(g.a, S, g.b);
-        const float gr = row[2 * width + c];
-        out[(int64_t)t * width + c] = from_f32<T>(S * (gr * sigmoid_f32(gr)));
+    for (int tb = t0; tb < t1; tb += kGruBatch) {
+        float zr[kGruBatch], ur[kGruBatch], gr[kGruBatch];
+#pragma unroll
+        for (int u = 0; u < kGruBatch; ++u) {
+            const float* row = proj + (int64_t)min(tb + u, t1 - 1) * 3 * width + c;
+            zr[u] = row[0];
+            ur[u] = row[width];
+            gr[u] = row[2 * width];
+        }
+#pragma unroll
+        for (int u = 0; u < kGruBatch; ++u) {
+            if (tb + u < t1) {
+                const GruStep g = mingru_gates(zr[u] + bzc, ur[u] + bxc);
+                S = fmaf(g.a, S, g.b);
+                out[(int64_t)(tb + u) * width + c] = from_f32<T>(S * (gr[u] * sigmoid_f32(gr[u])));
+            }
+        }
     }
     *st = S;
 }
@@ -69,11 +82,22 @@ __global__ void mingru_tile_summary_kernel(const float* __restrict__ proj, const
     if (t1 > t0) {
         if (row0 == 0 && positions[t0] != 0) carried = state[(int64_t)slots[seq] * width + c];
         const float bzc = bz[c], bxc = bx[c];
-        for (int t = t0; t < t1; ++t) {
-            const float* row = proj + (int64_t)t * 3 * width;
-            const GruStep g = mingru_gates(row[c] + bzc, row[width + c] + bxc);
-            B = fmaf(g.a, B, g.b);
-            A *= g.a;
+        for (int tb = t0; tb < t1; tb += kGruBatch) {
+            float zr[kGruBatch], ur[kGruBatch];
+#pragma unroll
+            for (int u = 0; u < kGruBatch; ++u) {
+                const float* row = proj + (int64_t)min(tb + u, t1 - 1) * 3 * width + c;
+                zr[u] = row[0];
+                ur[u] = row[width];
+            }
+#pragma unroll
+            for (int u = 0; u < kGruBatch; ++u) {
+                if (tb + u < t1) {
+                    const GruStep g = mingru_gates(zr[u] + bzc, ur[u] + bxc);
+                    B = fmaf(g.a, B, g.b);
+                    A *= g.a;
+                }
+            }
         }
     }
     float* s = summary + (int64_t)tile * 3 * width + c;
@@ -102,12 +126,23 @@ __global__ void mingru_tile_apply_kernel(const float* __restrict__ proj, const f
         S = fmaf(s[0], S, s[width]);
     }
     const float bzc = bz[c], bxc = bx[c];
-    for (int t = t0; t < t1; ++t) {
-        const float* row = proj + (int64_t)t * 3 * width;
-        const GruStep g = mingru_gates(row[c] + bzc, row[width + c] + bxc);
-        S = fmaf(g.a, S, g.b);
-        const float gr = row[2 * width + c];
-        out[(int64_t)t * width + c] = from_f32<T>(S * (gr * sigmoid_f32(gr)));
+    for (int tb = t0; tb < t1; tb += kGruBatch) {
+        float zr[kGruBatch], ur[kGruBatch], gr[kGruBatch];
+#pragma unroll
+        for (int u = 0; u < kGruBatch; ++u) {
+            const float* row = proj + (int64_t)min(tb + u, t1 - 1) * 3 * width + c;
+            zr[u] = row[0];
+            ur[u] = row[width];
+            gr[u] = row[2 * width];
+        }
+#pragma unroll
+        for (int u = 0; u < kGruBatch; ++u) {
+            if (tb + u < t1) {
+                const GruStep g = mingru_gates(zr[u] + bzc, ur[u] + bxc);
+                S = fmaf(g.a, S, g.b);
+                out[(int64_t)(tb + u) * width + c] = from_f32<T>(S * (gr[u] * sigmoid_f32(gr[u])));
+            }
+        }
     }
     if (t1 == end) state[(int64_t)slots[seq] * width + c] = S;
 }

@@ -60,7 +60,7 @@ _SIGNATURES = {
     "cpm_latent_norm_store": [_P, _P, _P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_float, c_int, _P],
     "cpm_head_project": [_P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P],
     "cpm_latent_attention": [_P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_float, c_int, _P],
-    "cpm_latent_attention_mma": [_P, _P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_float, c_int, _P],
+    "cpm_latent_attention_mma": [_P, _P, _P, c_int, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_float, c_int, _P],
 }
 
 # source files whose kernels follow page tables; the checked build (CPMCU_CHECK_BOUNDS=1) keeps a record per file

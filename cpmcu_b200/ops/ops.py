@@ -287,9 +287,15 @@ class Ops:
                                              self._stream()), "latent_norm_store")
         return cq
 
+    HEAD_PROJECT_LIBRARY_MIN_TOKENS = 64      # from this many tokens on, the per-head maps of the bf16 path are batched library products
+
+    def head_project_by_library(self, n_tokens: int) -> bool:
+        return self.code == BF16 and n_tokens >= self.HEAD_PROJECT_LIBRARY_MIN_TOKENS
+
     def head_project(self, x: torch.Tensor, w: torch.Tensor, n_heads: int, out_f32: bool) -> torch.Tensor:
         """x [tokens, heads * k] (or [tokens, heads, k]; fp32 or the compute dtype) times w [heads, k, n] head by
-        head -> [tokens, heads, n], fp32 or the compute dtype."""
+        head -> [tokens, heads, n], fp32 or the compute dtype.  Many tokens of bf16 input go to the library's batched
+        product (one product per head over strided views), few tokens and the 32-bit path to this library's kernel."""
         self._act(w, "per-head matrices")
         n_tok = x.shape[0]
         H, K, N = w.shape
@@ -299,6 +305,11 @@ class Ops:
         if not in_f32 and x.dtype != self.dtype:
             raise ValueError("head_project: the input must be fp32 or the compute dtype")
         out = self.empty(n_tok, H, N, dtype=torch.float32 if out_f32 else self.dtype)
+        if self.head_project_by_library(n_tok) and not in_f32:
+            by_head = torch.bmm(x.view(n_tok, H, K).transpose(0, 1), w, out_dtype=out.dtype) if out_f32 else \
+                torch.bmm(x.view(n_tok, H, K).transpose(0, 1), w)
+            out.copy_(by_head.transpose(0, 1))
+            return out
         check(self.lib.cpm_head_project(_ptr(x), _ptr(w), _ptr(out), n_tok, H, K, N, 1 if in_f32 else 0,
                                         1 if out_f32 else 0, self.code, self._stream()), f"head_project ({K} -> {N})")
         return out
@@ -312,15 +323,21 @@ class Ops:
         keys = min(window, ctx.max_kv_len) if window else ctx.max_kv_len      # in a recorded step an upper bound
         return max(1, min(16, self.sm_count // blocks, ((keys + 31) // 32) // 4))
 
+    def latent_attention_on_tensor_cores(self, rank: int) -> bool:
+        return self.code == BF16 and rank % 16 == 0 and rank <= 512
+
     def latent_attention(self, ctx, q_lat: torch.Tensor, lane, scale: float, window: int = 0,
-                         n_splits: Optional[int] = None, tensor_cores: Optional[bool] = None) -> torch.Tensor:
+                         n_splits: Optional[int] = None, tensor_cores: Optional[bool] = None,
+                         out_compute_dtype: bool = False) -> torch.Tensor:
         """q_lat fp32 [tokens, heads, rank] over the lane's cached latents (one row per token, shared by all heads
-        as key and as value) -> fp32 [tokens, heads, rank], the softmax-weighted sums of latents.  bf16 latents of a
-        rank that is a multiple of 16 go to the tensor-core kernel (``tensor_cores`` False keeps the fp32 kernel)."""
+        as key and as value) -> [tokens, heads, rank], the softmax-weighted sums of latents, fp32 (or, from the
+        tensor-core kernel with ``out_compute_dtype``, bf16).  bf16 latents of a rank that is a multiple of 16 go to the
+        tensor-core kernel (``tensor_cores`` False keeps the fp32 kernel)."""
         self._f32(q_lat, "latent queries")
         n, H, R = q_lat.shape
-        out = self.empty(n, H, R, dtype=torch.float32)
-        mma_ok = self.code == BF16 and R % 16 == 0 and R <= 512
+        mma_ok = self.latent_attention_on_tensor_cores(R)
+        narrow = bool(out_compute_dtype) and mma_ok and tensor_cores is not False
+        out = self.empty(n, H, R, dtype=self.dtype if narrow else torch.float32)
         if tensor_cores and not mma_ok:
             raise ValueError("the tensor-core latent attention takes bf16 latents of a rank that is a multiple of 16 up to 512")
         if mma_ok and tensor_cores is not False:
@@ -329,7 +346,7 @@ class Ops:
             scratch = None
             if n_splits > 1:
                 scratch = self.empty(int(self.lib.cpm_latent_attention_scratch_floats(n, H, R, n_splits)), dtype=torch.float32)
-            check(self.lib.cpm_latent_attention_mma(_ptr(q_lat), _ptr(lane.k), _ptr(out), _ptr(scratch), _ptr(ctx.positions),
+            check(self.lib.cpm_latent_attention_mma(_ptr(q_lat), _ptr(lane.k), _ptr(out), 1 if narrow else 0, _ptr(scratch), _ptr(ctx.positions),
                                                     _ptr(ctx.token_seq), _ptr(ctx.slot_dev), _ptr(lane.page_table),
                                                     lane.page_table.shape[1], int(window), n, H, R, float(scale), n_splits,
                                                     self._stream()), f"latent attention on tensor cores (rank {R}, {H} heads)")

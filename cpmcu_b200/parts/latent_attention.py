@@ -76,6 +76,8 @@ class LatentAttention(Mixer):
         c_q = ops.latent_norm_store(ctx, down, self.g_q, self.g_kv, lane, self.q_rank, self.kv_rank, self.eps, writes_cache)
         q = ops.linear(c_q, self.w_uq)                                                   # [tokens, heads * dim]
         q_lat = ops.head_project(q, self.w_uk, self.n_heads, out_f32=True)               # [tokens, heads, kv_rank], 32-bit
-        o_lat = ops.latent_attention(ctx, q_lat, lane, self.scale, self.window)          # [tokens, heads, kv_rank], 32-bit
+        # [tokens, heads, kv_rank]: 32-bit, unless the map that follows is a library product of many tokens, which takes bf16
+        narrow = ops.head_project_by_library(ctx.n_tokens) and ops.latent_attention_on_tensor_cores(self.kv_rank)
+        o_lat = ops.latent_attention(ctx, q_lat, lane, self.scale, self.window, out_compute_dtype=narrow)
         o = ops.head_project(o_lat, self.w_uv, self.n_heads, out_f32=False)              # [tokens, heads * vdim]
         return ops.linear(o.view(ctx.n_tokens, self.n_heads * self.vd), self.w_o)
