@@ -677,9 +677,16 @@ def reravik_kernels(z: dict, pk: dict, context: int, batch: int) -> dict:
         note(f"{phase}/latent_attention", timed(lambda: ops.latent_attention(ctx, q_lat, latent.lane(0), d ** -0.5, win)),
              nbytes=(sum(min(win, s + nq) for nq, s in zip(q_lens, starts)) * R * 2.0 + n * H * R * 8.0) if phase == "decode" else 0.0,
              flops=4.0 * H * R * sum(keys), like="attention")
-        o_lat = ops.latent_attention(ctx, q_lat, latent.lane(0), d ** -0.5, win)
+        narrow = ops.head_project_by_library(n)            # as the mixer does: bf16 weighted latents for the library product
+        o_lat = ops.latent_attention(ctx, q_lat, latent.lane(0), d ** -0.5, win, out_compute_dtype=narrow)
         note(f"{phase}/head_project latent->values", timed(lambda: ops.head_project(o_lat, w_uv, H, out_f32=False)),
-             nbytes=n * H * (R * 4.0 + vd * 2.0) + H * vd * R * 2.0, flops=2.0 * n * H * vd * R)
+             nbytes=n * H * (R * (2.0 if narrow else 4.0) + vd * 2.0) + H * vd * R * 2.0, flops=2.0 * n * H * vd * R)
+        gu_w = torch.randn(2 * z["ff"], W, device=dev).bfloat16()
+        yy = torch.randn(n, W, device=dev).bfloat16()
+        note(f"{phase}/gate_up product with tanh-GELU", timed(lambda: ops.gated_linear(yy, gu_w, 8, 1)),
+             nbytes=2.0 * (2 * z["ff"] * W + n * W + n * z["ff"]), flops=4.0 * n * z["ff"] * W, like="gate_up with SiLU")
+        note(f"{phase}/gate_up product with SiLU (dense model)", timed(lambda: ops.gated_linear(yy, gu_w, 8, 0)),
+             nbytes=2.0 * (2 * z["ff"] * W + n * W + n * z["ff"]), flops=4.0 * n * z["ff"] * W)
         qd = torch.randn(n, H, d, device=dev).bfloat16()
         all_keys = [s + j + 1 for nq, s in zip(q_lens, starts) for j in range(nq)]
         note(f"{phase}/attention (dense model, 2 kv heads, no window)", timed(lambda: ops.attention(ctx, qd, dl, 2, d ** -0.5)),

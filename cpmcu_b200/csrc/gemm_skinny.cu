@@ -17,7 +17,7 @@
 // the gated activation as a kernel of its own (src/model/activation.cuh:6-18).
 #include "common.cuh"
 
-enum : int { EPI_BF16 = 0, EPI_F32 = 1, EPI_SILU = 2 };
+enum : int { EPI_BF16 = 0, EPI_F32 = 1, EPI_SILU = 2, EPI_GELU = 3 };      // 2, 3: act(gate) * up with SiLU, with the tanh form of GELU
 
 // 128-byte lines of each weight row a block asks L2 for at its start (and, under programmatic dependent
 // launch, before it waits for the kernel ahead of it).  Eight lines bring the first loads of the main loop
@@ -104,7 +104,7 @@ skinny_gemm_kernel(const bf16* __restrict__ W, const bf16* __restrict__ X, void*
         red[warp][g + 8][nt * 8 + 2 * j + 1] = acc[nt][3];
     }
     __syncthreads();
-    if (EPI == EPI_SILU) {
+    if (EPI == EPI_SILU || EPI == EPI_GELU) {
         // rows 0..7 are gate, rows 8..15 up, of features (n0 / 2) + 0..7
         for (int o = threadIdx.x; o < 8 * MT; o += kSkinnyWarps * 32) {
             const int f = o & 7, tok = o >> 3;
@@ -117,8 +117,14 @@ skinny_gemm_kernel(const bf16* __restrict__ W, const bf16* __restrict__ X, void*
             }
             const int feature = (n0 >> 1) + f;
             if (feature < (N >> 1)) {
-                const float s = 1.0f / (1.0f + expf(-gate));
-                reinterpret_cast<bf16*>(out)[(int64_t)tok * (N >> 1) + feature] = __float2bfloat16_rn(gate * s * up);
+                float act;
+                if (EPI == EPI_GELU) {
+                    act = 0.5f * gate * (1.0f + tanhf(0.7978845608028654f * (gate + 0.044715f * gate * gate * gate)));
+                } else {
+                    const float s = 1.0f / (1.0f + expf(-gate));
+                    act = gate * s;
+                }
+                reinterpret_cast<bf16*>(out)[(int64_t)tok * (N >> 1) + feature] = __float2bfloat16_rn(act * up);
             }
         }
     } else {
@@ -148,6 +154,7 @@ static int launch_skinny(const void* W, const void* X, void* out, int M, int N, 
     if (epilogue == EPI_BF16) return launch_skinny_epi<NT, EPI_BF16>(W, X, out, M, N, K, alpha, stream);
     if (epilogue == EPI_F32) return launch_skinny_epi<NT, EPI_F32>(W, X, out, M, N, K, alpha, stream);
     if (epilogue == EPI_SILU) return launch_skinny_epi<NT, EPI_SILU>(W, X, out, M, N, K, alpha, stream);
+    if (epilogue == EPI_GELU) return launch_skinny_epi<NT, EPI_GELU>(W, X, out, M, N, K, alpha, stream);
     return CPM_BAD_ARGUMENT;
 }
 
@@ -157,7 +164,7 @@ CPM_API int cpm_gemm_skinny_bf16(const void* W, const void* X, void* out, int M,
                                  int epilogue, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return CPM_OK;
     if (M > 16 || K <= 0 || K % 32 != 0) return CPM_BAD_ARGUMENT;
-    if (epilogue == EPI_SILU && N % 16 != 0) return CPM_BAD_ARGUMENT;
+    if ((epilogue == EPI_SILU || epilogue == EPI_GELU) && N % 16 != 0) return CPM_BAD_ARGUMENT;
     if (M <= 8) return launch_skinny<1>(W, X, out, M, N, K, alpha, epilogue, stream);
     return launch_skinny<2>(W, X, out, M, N, K, alpha, epilogue, stream);
 }

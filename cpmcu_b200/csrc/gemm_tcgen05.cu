@@ -44,7 +44,18 @@ constexpr int kThreads = 192;                                   // 6 warps
 constexpr int kTmemCols = 512;
 constexpr int kBandTiles = 16;                                  // 2048 rows of A are shared by the blocks that run together
 
-enum : int { EPI_BF16 = 0, EPI_SILU = 2 };
+enum : int { EPI_BF16 = 0, EPI_SILU = 2, EPI_GELU = 3 };      // 2, 3: act(gate) * up with SiLU, with the tanh form of GELU
+
+// act(g) * u of the gated epilogues; fast exponential and hyperbolic tangent: the result is rounded to bf16.
+template <int EPI>
+__device__ __forceinline__ float gated_value(float g, float u) {
+    if (EPI == EPI_GELU) {
+        float th;
+        asm("tanh.approx.f32 %0, %1;" : "=f"(th) : "f"(0.7978845608028654f * (g + 0.044715f * g * g * g)));
+        return 0.5f * g * (1.0f + th) * u;
+    }
+    return __fdividef(g, 1.0f + __expf(-g)) * u;
+}
 enum : int { ERR_NONE = 0, ERR_FULL_WAIT = 1, ERR_EMPTY_WAIT = 2, ERR_ACC_FULL_WAIT = 3, ERR_ACC_EMPTY_WAIT = 4 };
 
 __device__ int g_error = 0;      // first error code any block has recorded since the last reset
@@ -76,11 +87,12 @@ __device__ __forceinline__ TileCoord tile_coord(int tile, int tiles_m, int tiles
 template <int EPI, int BN = kBlockN>
 __device__ __forceinline__ void epilogue_tile(bf16* __restrict__ out, uint32_t taddr, unsigned char* staging, int row0, int n0,
                                               int M, int N, int lane) {
-    constexpr int kLoadsPerPass = EPI == EPI_SILU ? 4 : 2;          // 32 accumulator columns each; a pass is 64 outputs
+    constexpr bool kGated = EPI == EPI_SILU || EPI == EPI_GELU;
+    constexpr int kLoadsPerPass = kGated ? 4 : 2;          // 32 accumulator columns each; a pass is 64 outputs
     constexpr int kLoads = BN / 32;                                 // the tile's accumulator columns, 32 at a time
     constexpr int kPasses = (kLoads + kLoadsPerPass - 1) / kLoadsPerPass;     // the last pass may be a part of one
-    const int ldo = EPI == EPI_SILU ? N >> 1 : N;
-    const int oc_tile = EPI == EPI_SILU ? n0 >> 1 : n0;
+    const int ldo = kGated ? N >> 1 : N;
+    const int oc_tile = kGated ? n0 >> 1 : n0;
     uint4* my_row = reinterpret_cast<uint4*>(staging + lane * 128);
 #pragma unroll 1
     for (int p = 0; p < kPasses; ++p) {
@@ -92,7 +104,7 @@ __device__ __forceinline__ void epilogue_tile(bf16* __restrict__ out, uint32_t t
             uint32_t v[32];
             tmem_load_32cols(taddr + (p * kLoadsPerPass + h) * 32, v);
             tmem_load_wait();
-            if (EPI == EPI_SILU) {
+            if (kGated) {
                 // columns: 8 gate, 8 up, 8 gate, 8 up of 16 consecutive features
                 uint32_t packed[8];
 #pragma unroll
@@ -101,8 +113,8 @@ __device__ __forceinline__ void epilogue_tile(bf16* __restrict__ out, uint32_t t
                     for (int i = 0; i < 8; i += 2) {
                         const float g0 = __uint_as_float(v[16 * q + i]), g1 = __uint_as_float(v[16 * q + i + 1]);
                         const float u0 = __uint_as_float(v[16 * q + 8 + i]), u1 = __uint_as_float(v[16 * q + 9 + i]);
-                        const float a = __fdividef(g0, 1.0f + __expf(-g0)) * u0;      // the result is rounded to bf16
-                        const float b = __fdividef(g1, 1.0f + __expf(-g1)) * u1;
+                        const float a = gated_value<EPI>(g0, u0);
+                        const float b = gated_value<EPI>(g1, u1);
                         const __nv_bfloat162 pk = __floats2bfloat162_rn(a, b);
                         packed[4 * q + i / 2] = *reinterpret_cast<const uint32_t*>(&pk);
                     }
@@ -539,6 +551,10 @@ CPM_API int cpm_gemm_bf16_tcgen05_pair(const void* A, const void* W, void* out, 
         if (N % 32 != 0) return CPM_BAD_ARGUMENT;
         return tc5::launch_pair<tc5::EPI_SILU>(A, W, out, M, N, K, n_blocks, stream);
     }
+    if (epilogue == tc5::EPI_GELU) {
+        if (N % 32 != 0) return CPM_BAD_ARGUMENT;
+        return tc5::launch_pair<tc5::EPI_GELU>(A, W, out, M, N, K, n_blocks, stream);
+    }
     if (epilogue != tc5::EPI_BF16 || N % 8 != 0) return CPM_BAD_ARGUMENT;
     return tc5::launch_pair<tc5::EPI_BF16>(A, W, out, M, N, K, n_blocks, stream);
 }
@@ -555,6 +571,10 @@ CPM_API int cpm_gemm_bf16_tcgen05(const void* A, const void* W, void* out, int M
     if (epilogue == tc5::EPI_SILU) {
         if (N % 32 != 0) return CPM_BAD_ARGUMENT;
         return tc5::launch<tc5::EPI_SILU>(A, W, out, M, N, K, n_blocks, stream);
+    }
+    if (epilogue == tc5::EPI_GELU) {
+        if (N % 32 != 0) return CPM_BAD_ARGUMENT;
+        return tc5::launch<tc5::EPI_GELU>(A, W, out, M, N, K, n_blocks, stream);
     }
     if (epilogue != tc5::EPI_BF16 || N % 8 != 0) return CPM_BAD_ARGUMENT;
     return tc5::launch<tc5::EPI_BF16>(A, W, out, M, N, K, n_blocks, stream);

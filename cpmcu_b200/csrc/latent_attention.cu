@@ -346,20 +346,22 @@ latent_attention_mma_kernel(const float* __restrict__ q, const bf16* __restrict_
     __syncthreads();
 
     const int vec_per_row = rank / 8;                                    // 16-byte pieces of a latent row
+    // a warp brings every fourth row of a tile (the row's address worked out once), its lanes the row's 16-byte pieces
     auto fetch = [&](int tile, int buf) {
         const int j0 = lo + tile * kMmaKeys;
         bf16* dst = Ks + buf * kMmaKeys * pitch;
-        for (int i = threadIdx.x; i < kMmaKeys * vec_per_row; i += blockDim.x) {
-            const int r = i / vec_per_row, v = i % vec_per_row;
+#pragma unroll
+        for (int rr = 0; rr < kMmaKeys / 4; ++rr) {
+            const int r = warp + 4 * rr;
             const int j = j0 + r;
             const bool real = j <= p;
             const bf16* src = cache;
             if (real) {
                 const int lp = j / kPageTokens;
                 const int page = pages_in_smem ? page_s[lp - first_page] : CPM_PAGE(pages, lp, max_pages);
-                src = cache + page_row_offset(page, 0, j % kPageTokens, 1, rank) + 8 * v;
+                src = cache + page_row_offset(page, 0, j % kPageTokens, 1, rank);
             }
-            cp_async_16(dst + r * pitch + 8 * v, src, real);
+            for (int v = lane; v < vec_per_row; v += 32) cp_async_16(dst + r * pitch + 8 * v, real ? src + 8 * v : src, real);
         }
         cp_async_commit();
     };
@@ -502,28 +504,41 @@ latent_attention_mma_kernel(const float* __restrict__ q, const bf16* __restrict_
     }
 }
 
+// One block per (token, head group, row of the tile): the shares' weights are worked out once, then the threads add up
+// the shares' columns.
 __global__ void latent_attention_merge_kernel(const float* __restrict__ scratch, void* __restrict__ out_any, int out_bf16, int n_heads,
                                               int rank, int n_splits) {
+    __shared__ float weight[64];
+    __shared__ float inv_l;
     pdl_launch_dependents();
     pdl_wait();
-    const int t = blockIdx.x, hg = blockIdx.y;
-    const float* base = scratch + ((int64_t)t * gridDim.y + hg) * n_splits * kMmaRows * (rank + 2);
-    for (int i = threadIdx.x; i < kMmaRows * rank; i += blockDim.x) {
-        const int r = i / rank, c = i % rank;
-        const int h = hg * kMmaRows + r;
-        if (h >= n_heads) continue;
+    const int t = blockIdx.x, hg = blockIdx.y, r = blockIdx.z;
+    const int h = hg * kMmaRows + r;
+    if (h >= n_heads) return;
+    const float* base = scratch + (((int64_t)t * gridDim.y + hg) * n_splits * kMmaRows + r) * (rank + 2);
+    const int64_t share = (int64_t)kMmaRows * (rank + 2);
+    if (threadIdx.x < 32) {
         float mx = -INFINITY;
-        for (int s = 0; s < n_splits; ++s) mx = fmaxf(mx, base[(s * kMmaRows + r) * (rank + 2) + rank]);
-        float l = 0.f, o = 0.f;
-        for (int s = 0; s < n_splits; ++s) {
-            const float* prow = base + (s * kMmaRows + r) * (rank + 2);
-            const float w = prow[rank] == -INFINITY ? 0.f : expf(prow[rank] - mx);
-            l = fmaf(prow[rank + 1], w, l);
-            o = fmaf(prow[c], w, o);
+        for (int s = threadIdx.x; s < n_splits; s += 32) mx = fmaxf(mx, base[s * share + rank]);
+        mx = warp_max(mx);
+        float l = 0.f;
+        for (int s = threadIdx.x; s < n_splits; s += 32) {
+            const float ms = base[s * share + rank];
+            const float w = ms == -INFINITY ? 0.f : expf(ms - mx);
+            weight[s] = w;
+            l = fmaf(base[s * share + rank + 1], w, l);
         }
-        const float res = l > 0.f ? o / l : 0.f;
-        if (out_bf16) static_cast<bf16*>(out_any)[((int64_t)t * n_heads + h) * rank + c] = __float2bfloat16_rn(res);
-        else static_cast<float*>(out_any)[((int64_t)t * n_heads + h) * rank + c] = res;
+        l = warp_sum(l);
+        if (threadIdx.x == 0) inv_l = l > 0.f ? 1.f / l : 0.f;
+    }
+    __syncthreads();
+    const int64_t o = ((int64_t)t * n_heads + h) * rank;
+    for (int c = threadIdx.x; c < rank; c += blockDim.x) {
+        float acc = 0.f;
+        for (int s = 0; s < n_splits; ++s) acc = fmaf(base[s * share + c], weight[s], acc);
+        const float res = acc * inv_l;
+        if (out_bf16) static_cast<bf16*>(out_any)[o + c] = __float2bfloat16_rn(res);
+        else static_cast<float*>(out_any)[o + c] = res;
     }
 }
 
@@ -546,7 +561,7 @@ static int launch_latent_mma(const float* q, const void* cache, void* out, int o
     cpm_launch(kLaunchAttention, kern, grid, 128, smem, stream, q, (const bf16*)cache, out, out_bf16, scratch, positions, token_seq, slots,
                page_table, max_pages, window, n_heads, rank, scale, n_splits);
     if (n_splits > 1)
-        cpm_launch(kLaunchCombine, latent_attention_merge_kernel, dim3(n_tokens, groups), 256, 0, stream, (const float*)scratch, out,
+        cpm_launch(kLaunchCombine, latent_attention_merge_kernel, dim3(n_tokens, groups, kMmaRows), 128, 0, stream, (const float*)scratch, out,
                    out_bf16, n_heads, rank, n_splits);
     return launch_status();
 }
@@ -556,7 +571,7 @@ CPM_API int cpm_latent_attention_mma(const float* q, const void* cache, void* ou
                                      const int* token_seq, const int* slots, const int* page_table, int max_pages, int window,
                                      int n_tokens, int n_heads, int rank, float scale, int n_splits, cudaStream_t stream) {
     if (n_tokens <= 0) return CPM_OK;
-    if (n_heads <= 0 || rank <= 0 || rank > 512 || rank % 16 || window < 0 || n_splits < 1 || n_splits > 65535) return CPM_BAD_ARGUMENT;
+    if (n_heads <= 0 || rank <= 0 || rank > 512 || rank % 16 || window < 0 || n_splits < 1 || n_splits > 64) return CPM_BAD_ARGUMENT;
     if (n_splits > 1 && scratch == nullptr) return CPM_BAD_ARGUMENT;
     if ((n_heads + kMmaRows - 1) / kMmaRows > 65535) return CPM_BAD_ARGUMENT;
     if (rank <= 128) return launch_latent_mma<4>(q, cache, out, out_bf16, scratch, positions, token_seq, slots, page_table, max_pages, window,

@@ -417,9 +417,11 @@ class Ops:
         else:
             torch.mm(a, w.t(), out_dtype=c.dtype, out=c)
 
-    def linear_tcgen05(self, a: torch.Tensor, w: torch.Tensor, gated: bool = False, pair: bool = False) -> torch.Tensor:
+    def linear_tcgen05(self, a: torch.Tensor, w: torch.Tensor, gated: bool = False, pair: bool = False,
+                       epilogue: int = 2) -> torch.Tensor:
         """a[M,K] @ w[N,K]^T on the tcgen05 tensor cores (TMA operands, TMEM accumulator); with ``gated`` the
-        weight is a gate_up matrix interleaved in blocks of 8 and the result is silu(gate) * up, [M, N/2].
+        weight is a gate_up matrix interleaved in blocks of 8 and the result is act(gate) * up, [M, N/2] (``epilogue`` 2:
+        SiLU, 3: the tanh form of GELU).
         ``pair``: two blocks work on one 256 x 256 tile (cta_group::2)."""
         self._act(a, "linear input")
         self._act(w, "linear weight")
@@ -427,7 +429,7 @@ class Ops:
         N = w.shape[0]
         out = self.empty(M, N // 2 if gated else N)
         entry = self.lib.cpm_gemm_bf16_tcgen05_pair if pair else self.lib.cpm_gemm_bf16_tcgen05
-        check(entry(_ptr(a), _ptr(w), _ptr(out), M, N, K, 2 if gated else 0, self.sm_count, self._stream()),
+        check(entry(_ptr(a), _ptr(w), _ptr(out), M, N, K, int(epilogue) if gated else 0, self.sm_count, self._stream()),
               f"tcgen05 matrix product [{M}x{K}] x [{N}x{K}]^T")
         return out
 
@@ -444,25 +446,29 @@ class Ops:
               "act_mul")
         return h
 
+    GATED_EPILOGUES = {0: 2, 1: 3}      # activation code -> the product kernels' gated epilogue (SiLU, tanh-GELU)
+
     def gated_linear(self, a: torch.Tensor, w_gate_up: torch.Tensor, interleave: int, activation: int = 0) -> torch.Tensor:
         """act(a @ gate^T) * (a @ up^T) for a gate_up matrix [2*inter, K] laid out as ``interleave`` says; the
-        activation is SiLU (code 0) or the tanh form of GELU (code 1)."""
+        activation is SiLU (code 0) or the tanh form of GELU (code 1).  The weight-streaming product (few rows) and the
+        tcgen05 product (many rows) apply it in their epilogues; otherwise a kernel of its own follows the product."""
         M, K = a.shape
-        if activation != 0:
-            return self.act_mul(self.linear(a, w_gate_up), interleave, activation)
+        epilogue = self.GATED_EPILOGUES[int(activation)]
         if interleave == 8 and self._skinny_ok(M, K, w_gate_up.shape[0]) and w_gate_up.shape[0] % 16 == 0:
             self._act(a, "linear input")
             self._act(w_gate_up, "gate_up weight")
             h = self.empty(M, w_gate_up.shape[0] // 2)
-            check(self.lib.cpm_gemm_skinny_bf16(_ptr(w_gate_up), _ptr(a), _ptr(h), M, w_gate_up.shape[0], K, 1.0, 2,
+            check(self.lib.cpm_gemm_skinny_bf16(_ptr(w_gate_up), _ptr(a), _ptr(h), M, w_gate_up.shape[0], K, 1.0, epilogue,
                                                 self._stream()), "gated skinny matrix product")
             return h
         few_tiles = M < 256 and w_gate_up.shape[0] // 256 < self.sm_count // 2     # a decode batch on a narrow model: too few blocks
         if (self.code == BF16 and interleave == 8 and self.use_tcgen05 and M >= self.TCGEN05_MIN_ROWS and K % 64 == 0
                 and w_gate_up.shape[0] % 32 == 0 and a.data_ptr() % 16 == 0 and not few_tiles):
             # many rows (prefill): the tcgen05 product applies the activation in its epilogue
-            return self.linear_tcgen05(a, w_gate_up, gated=True, pair=self.tcgen05_pair)
-        return self.silu_mul(self.linear(a, w_gate_up), interleave)
+            return self.linear_tcgen05(a, w_gate_up, gated=True, pair=self.tcgen05_pair, epilogue=epilogue)
+        if activation == 0:
+            return self.silu_mul(self.linear(a, w_gate_up), interleave)
+        return self.act_mul(self.linear(a, w_gate_up), interleave, activation)
 
     # ---- attention ----
     def rope_store(self, qkv: torch.Tensor, n_heads: int, n_kv: int, d: int, positions: torch.Tensor,

@@ -494,3 +494,22 @@ def test_latent_attention_on_tensor_cores_against_the_fp32_kernel(rank, heads, w
         got = ops.latent_attention(ctx, q, lane, 0.11, window, n_splits=n_splits, tensor_cores=True)
         err = (got - want).abs().max() / want.abs().max()
         assert float(err) < 2e-2, (n_splits, float(err))
+
+
+@pytest.mark.parametrize("rows", [3, 8, 12, 40, 300])
+def test_gated_products_with_tanh_gelu(rows):
+    """The gate_up product with the tanh form of GELU through every path the row count selects (the weight-streaming
+    kernel, the tcgen05 kernel, the library product followed by the activation kernel) against fp64."""
+    from cpmcu_b200.ops.ops import Ops
+
+    ops = Ops(torch.bfloat16)
+    g = torch.Generator().manual_seed(rows)
+    K, inter = 128, 160 * 128                          # enough tiles for the tcgen05 path at 300 rows
+    gate = (torch.randn(inter, K, generator=g) * 0.2).bfloat16()
+    up = (torch.randn(inter, K, generator=g) * 0.2).bfloat16()
+    w = torch.stack([gate.view(inter // 8, 8, K), up.view(inter // 8, 8, K)], dim=1).reshape(2 * inter, K).contiguous().cuda()
+    a = torch.randn(rows, K, generator=g).bfloat16().cuda()
+    want = plain.gelu_tanh(a.double().cpu() @ gate.double().T) * (a.double().cpu() @ up.double().T)
+    got = ops.gated_linear(a, w, 8, 1).double().cpu()
+    assert float(((got - want).abs() / (1 + want.abs())).max()) < 2e-2
+    ops.raise_on_kernel_error()
