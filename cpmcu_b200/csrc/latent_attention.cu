@@ -310,7 +310,7 @@ latent_attention_mma_kernel(const float* __restrict__ q, const bf16* __restrict_
     __shared__ int page_s[kPageSlots];
     const int pitch = rank + 8;                                          // bf16 elements per latent row in shared memory
     bf16* Ks = reinterpret_cast<bf16*>(lm_smem);                         // [2][32][pitch]
-    float* Ss = reinterpret_cast<float*>(Ks + 2 * kMmaKeys * pitch);     // [4 warps][16][33]
+    float* Ss = reinterpret_cast<float*>(Ks + 2 * kMmaKeys * pitch);     // [4 warps][16 values][32 lanes]
     pdl_launch_dependents();
     pdl_wait();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, tg = lane & 3;
@@ -366,10 +366,18 @@ latent_attention_mma_kernel(const float* __restrict__ q, const bf16* __restrict_
         cp_async_commit();
     };
 
+    // softmax statistics in the base-2 domain: scores are multiplied by scale * log2(e) and weights are exp2
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};             // rows g and g + 8
     float acc[NT][4];
 #pragma unroll
     for (int i = 0; i < NT; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
+    const float scale2 = scale * 1.4426950408889634f;
+    // this lane's row addresses of the ldmatrix loads, relative to a tile: four 8 x 8 pieces at once.
+    // scores (keys as the n side): pieces (keys 0-7, k 0-7), (keys 0-7, k 8-15), (keys 8-15, k 0-7), (keys 8-15, k 8-15)
+    const int s_off = ((lane >> 4) * 8 + (lane & 7)) * pitch + 8 * ((lane >> 3) & 1);
+    // weighted sum (keys as the k side, transposed on the way): pieces keys 0-7, 8-15, 16-23, 24-31 of 8 columns
+    const int v_off = lane * pitch + 8 * warp;
+    float* mine = Ss + warp * 16 * 32;                                   // [16 values][32 lanes] of this warp's partial scores
 
     if (tile0 < tile1) fetch(tile0, 0);
     for (int tile = tile0; tile < tile1; ++tile) {
@@ -383,91 +391,99 @@ latent_attention_mma_kernel(const float* __restrict__ q, const bf16* __restrict_
         }
         __syncthreads();                                                 // the tile is there for every warp
         const bf16* Kt = Ks + buf * kMmaKeys * pitch;
-        {   // partial scores of all 32 keys over this warp's part of the rank
-            float c[4][4];
+        // partial scores of all 32 keys over this warp's part of the rank: c[n] is the 16 x 8 piece of keys 8n .. 8n + 7
+        float c[4][4];
 #pragma unroll
-            for (int n = 0; n < 4; ++n) c[n][0] = c[n][1] = c[n][2] = c[n][3] = 0.f;
+        for (int n = 0; n < 4; ++n) c[n][0] = c[n][1] = c[n][2] = c[n][3] = 0.f;
+        {
+            const uint32_t s_base = (uint32_t)__cvta_generic_to_shared(Kt + s_off);
 #pragma unroll
             for (int i = 0; i < KS; ++i) {
                 const int ks = warp + 4 * i;
                 if (ks < k_steps) {
 #pragma unroll
-                    for (int n = 0; n < 4; ++n) {
-                        const bf16* krow = Kt + (8 * n + g) * pitch + ks * 16 + 2 * tg;
-                        mma_bf16_16816(c[n], qa[i], *reinterpret_cast<const uint32_t*>(krow), *reinterpret_cast<const uint32_t*>(krow + 8));
+                    for (int np = 0; np < 2; ++np) {
+                        uint32_t b[4];
+                        const uint32_t addr = s_base + (uint32_t)((16 * np * pitch + ks * 16) * sizeof(bf16));
+                        asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                                     : "=r"(b[0]), "=r"(b[1]), "=r"(b[2]), "=r"(b[3]) : "r"(addr));
+                        mma_bf16_16816(c[2 * np], qa[i], b[0], b[1]);
+                        mma_bf16_16816(c[2 * np + 1], qa[i], b[2], b[3]);
                     }
                 }
             }
-            float* mine = Ss + warp * kMmaRows * 33;
-#pragma unroll
-            for (int n = 0; n < 4; ++n) {
-                const int col = 8 * n + 2 * tg;
-                mine[g * 33 + col] = c[n][0];
-                mine[g * 33 + col + 1] = c[n][1];
-                mine[(g + 8) * 33 + col] = c[n][2];
-                mine[(g + 8) * 33 + col + 1] = c[n][3];
-            }
         }
+        // the four warps' partial scores are added lane by lane: every warp ends up with the whole 16 x 32 tile in the
+        // layout of its own accumulators, which is also the layout of the A fragments of the weighted sum
+#pragma unroll
+        for (int n = 0; n < 4; ++n)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) mine[(4 * n + e) * 32 + lane] = c[n][e];
         __syncthreads();
-        // softmax of the tile, kept by every warp alike; a thread holds, for rows g and g + 8, the columns
-        // 2tg, 2tg+1, 2tg+8, 2tg+9 of both halves of 16 keys: its A fragments of the weighted sum
-        float s[2][2][4];
+        // (in the same order in every warp, so that all warps hold the very same sums and statistics)
 #pragma unroll
-        for (int half = 0; half < 2; ++half)
+        for (int n = 0; n < 4; ++n)
 #pragma unroll
-            for (int r = 0; r < 2; ++r)
+            for (int e = 0; e < 4; ++e) {
+                const float* cell = Ss + (4 * n + e) * 32 + lane;
+                c[n][e] = (cell[0] + cell[16 * 32]) + (cell[2 * 16 * 32] + cell[3 * 16 * 32]);
+            }
+        // c[n][0], c[n][1]: row g, keys 8n + 2tg, + 1;  c[n][2], c[n][3]: row g + 8
+        const bool ragged = j0 + kMmaKeys - 1 > p;                       // the block's last tile may reach past the query
 #pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const int col = 16 * half + 2 * tg + (e & 1) + 8 * (e >> 1);
-                    const float* cell = Ss + (g + 8 * r) * 33 + col;
-                    const float v = cell[0] + cell[kMmaRows * 33] + cell[2 * kMmaRows * 33] + cell[3 * kMmaRows * 33];
-                    s[half][r][e] = j0 + col <= p ? v * scale : -INFINITY;
-                }
-        uint32_t pa[2][4];
+        for (int n = 0; n < 4; ++n)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float v = c[n][e] * scale2;
+                c[n][e] = (ragged && j0 + 8 * n + 2 * tg + (e & 1) > p) ? -INFINITY : v;
+            }
+        float corr[2];
 #pragma unroll
         for (int r = 0; r < 2; ++r) {
             float mx = -INFINITY;
 #pragma unroll
-            for (int half = 0; half < 2; ++half)
-#pragma unroll
-                for (int e = 0; e < 4; ++e) mx = fmaxf(mx, s[half][r][e]);
+            for (int n = 0; n < 4; ++n) mx = fmaxf(mx, fmaxf(c[n][2 * r], c[n][2 * r + 1]));
             mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
             mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-            const float m_new = fmaxf(m[r], mx);
-            const float corr = (m[r] == -INFINITY) ? 0.f : expf(m[r] - m_new);
+            const float m_new = fmaxf(m[r], mx);                         // finite: a tile holds at least one visible key
+            corr[r] = exp2f(m[r] - m_new);                               // 0 at the first tile (m = -inf)
             float sum = 0.f;
 #pragma unroll
-            for (int half = 0; half < 2; ++half)
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const float pv = (m_new == -INFINITY) ? 0.f : expf(s[half][r][e] - m_new);
-                    s[half][r][e] = pv;
-                    sum += pv;
-                }
+            for (int n = 0; n < 4; ++n) {
+                c[n][2 * r] = exp2f(c[n][2 * r] - m_new);
+                c[n][2 * r + 1] = exp2f(c[n][2 * r + 1] - m_new);
+                sum += c[n][2 * r] + c[n][2 * r + 1];
+            }
             sum += __shfl_xor_sync(0xffffffffu, sum, 1);
             sum += __shfl_xor_sync(0xffffffffu, sum, 2);
-            l[r] = l[r] * corr + sum;
+            l[r] = l[r] * corr[r] + sum;
             m[r] = m_new;
-#pragma unroll
-            for (int i = 0; i < NT; ++i) { acc[i][2 * r] *= corr; acc[i][2 * r + 1] *= corr; }
         }
+        if (__any_sync(0xffffffffu, corr[0] != 1.f || corr[1] != 1.f)) {
+#pragma unroll
+            for (int i = 0; i < NT; ++i) {
+                acc[i][0] *= corr[0]; acc[i][1] *= corr[0];
+                acc[i][2] *= corr[1]; acc[i][3] *= corr[1];
+            }
+        }
+        uint32_t pa[2][4];
 #pragma unroll
         for (int half = 0; half < 2; ++half) {
-            pa[half][0] = pack_bf16(s[half][0][0], s[half][0][1]);      // row g,     keys 2tg, 2tg+1
-            pa[half][1] = pack_bf16(s[half][1][0], s[half][1][1]);      // row g + 8
-            pa[half][2] = pack_bf16(s[half][0][2], s[half][0][3]);      // row g,     keys 2tg+8, 2tg+9
-            pa[half][3] = pack_bf16(s[half][1][2], s[half][1][3]);      // row g + 8
+            pa[half][0] = pack_bf16(c[2 * half][0], c[2 * half][1]);          // row g,     keys 16 half + 2tg, + 1
+            pa[half][1] = pack_bf16(c[2 * half][2], c[2 * half][3]);          // row g + 8
+            pa[half][2] = pack_bf16(c[2 * half + 1][0], c[2 * half + 1][1]);  // row g,     keys 16 half + 8 + 2tg, + 1
+            pa[half][3] = pack_bf16(c[2 * half + 1][2], c[2 * half + 1][3]);  // row g + 8
         }
+        {
+            const uint32_t v_base = (uint32_t)__cvta_generic_to_shared(Kt + v_off);
 #pragma unroll
-        for (int i = 0; i < NT; ++i) {
-            const int col0 = 8 * (warp + 4 * i);
-            if (col0 < rank) {
-#pragma unroll
-                for (int half = 0; half < 2; ++half) {
-                    uint32_t b0, b1;
-                    const uint32_t addr = (uint32_t)__cvta_generic_to_shared(Kt + (16 * half + (lane & 15)) * pitch + col0);
-                    asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];" : "=r"(b0), "=r"(b1) : "r"(addr));
-                    mma_bf16_16816(acc[i], pa[half], b0, b1);
+            for (int i = 0; i < NT; ++i) {
+                if (8 * (warp + 4 * i) < rank) {
+                    uint32_t b[4];
+                    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                                 : "=r"(b[0]), "=r"(b[1]), "=r"(b[2]), "=r"(b[3]) : "r"(v_base + (uint32_t)(32 * i * sizeof(bf16))));
+                    mma_bf16_16816(acc[i], pa[0], b[0], b[1]);
+                    mma_bf16_16816(acc[i], pa[1], b[2], b[3]);
                 }
             }
         }
@@ -524,7 +540,7 @@ __global__ void latent_attention_merge_kernel(const float* __restrict__ scratch,
         float l = 0.f;
         for (int s = threadIdx.x; s < n_splits; s += 32) {
             const float ms = base[s * share + rank];
-            const float w = ms == -INFINITY ? 0.f : expf(ms - mx);
+            const float w = ms == -INFINITY ? 0.f : exp2f(ms - mx);      // the shares' maxima are base-2 logarithms
             weight[s] = w;
             l = fmaf(base[s * share + rank + 1], w, l);
         }
@@ -552,7 +568,7 @@ static int launch_latent_mma(const float* q, const void* cache, void* out, int o
                              const int* token_seq, const int* slots, const int* page_table, int max_pages, int window,
                              int n_tokens, int n_heads, int rank, float scale, int n_splits, cudaStream_t stream) {
     static bool smem_done[kMaxDevices];
-    const size_t smem = (size_t)2 * kMmaKeys * (rank + 8) * sizeof(bf16) + (size_t)4 * kMmaRows * 33 * sizeof(float);
+    const size_t smem = (size_t)2 * kMmaKeys * (rank + 8) * sizeof(bf16) + (size_t)4 * 16 * 32 * sizeof(float);
     auto kern = latent_attention_mma_kernel<NT>;
     if (smem > 48 * 1024)
         if (int e = ensure_dynamic_smem(kern, (int)smem, smem_done)) return e;
