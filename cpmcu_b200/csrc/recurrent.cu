@@ -19,7 +19,7 @@
 
 __device__ __forceinline__ float sigmoid_f32(float v) { return 1.0f / (1.0f + expf(-v)); }
 
-constexpr int kGruBatch = 8;      // tokens whose projections are loaded before the first is used
+constexpr int kGruBatch = 16;     // tokens whose projections are loaded before the first is used
 
 struct GruStep { float a, b; };      // S <- a * S + b
 
