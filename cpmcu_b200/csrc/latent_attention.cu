@@ -278,12 +278,19 @@ __device__ __forceinline__ void mma_bf16_16816(float* c, const uint32_t* a, uint
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
+__device__ __forceinline__ float fast_exp2(float x) {      // 2^x, about two units in the last place; 0 for x = -inf
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<const uint32_t*>(&v);
 }
 
-constexpr int kPageSlots = 1024;      // page numbers of a block's keys kept in shared memory (beyond: read from the table)
+constexpr int kPageSlots = 256;       // page numbers of a block's keys kept in shared memory (beyond: read from the table);
+                                      // 1 KiB, so that three blocks of the rank-512 kernel fit one SM's shared memory
 
 __device__ __forceinline__ void cp_async_16(void* smem, const void* gmem, bool real) {
     const uint32_t dst = (uint32_t)__cvta_generic_to_shared(smem);
@@ -430,13 +437,13 @@ latent_attention_mma_kernel(const float* __restrict__ q, const bf16* __restrict_
             }
         // c[n][0], c[n][1]: row g, keys 8n + 2tg, + 1;  c[n][2], c[n][3]: row g + 8
         const bool ragged = j0 + kMmaKeys - 1 > p;                       // the block's last tile may reach past the query
+        if (ragged) {
 #pragma unroll
-        for (int n = 0; n < 4; ++n)
+            for (int n = 0; n < 4; ++n)
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const float v = c[n][e] * scale2;
-                c[n][e] = (ragged && j0 + 8 * n + 2 * tg + (e & 1) > p) ? -INFINITY : v;
-            }
+                for (int e = 0; e < 4; ++e)
+                    if (j0 + 8 * n + 2 * tg + (e & 1) > p) c[n][e] = -INFINITY;
+        }
         float corr[2];
 #pragma unroll
         for (int r = 0; r < 2; ++r) {
@@ -445,13 +452,13 @@ latent_attention_mma_kernel(const float* __restrict__ q, const bf16* __restrict_
             for (int n = 0; n < 4; ++n) mx = fmaxf(mx, fmaxf(c[n][2 * r], c[n][2 * r + 1]));
             mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
             mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-            const float m_new = fmaxf(m[r], mx);                         // finite: a tile holds at least one visible key
-            corr[r] = exp2f(m[r] - m_new);                               // 0 at the first tile (m = -inf)
+            const float m_new = fmaxf(m[r], mx * scale2);                // finite: a tile holds at least one visible key
+            corr[r] = fast_exp2(m[r] - m_new);                           // 0 at the first tile (m = -inf)
             float sum = 0.f;
 #pragma unroll
             for (int n = 0; n < 4; ++n) {
-                c[n][2 * r] = exp2f(c[n][2 * r] - m_new);
-                c[n][2 * r + 1] = exp2f(c[n][2 * r + 1] - m_new);
+                c[n][2 * r] = fast_exp2(fmaf(c[n][2 * r], scale2, -m_new));
+                c[n][2 * r + 1] = fast_exp2(fmaf(c[n][2 * r + 1], scale2, -m_new));
                 sum += c[n][2 * r] + c[n][2 * r + 1];
             }
             sum += __shfl_xor_sync(0xffffffffu, sum, 1);
@@ -570,8 +577,14 @@ static int launch_latent_mma(const float* q, const void* cache, void* out, int o
     static bool smem_done[kMaxDevices];
     const size_t smem = (size_t)2 * kMmaKeys * (rank + 8) * sizeof(bf16) + (size_t)4 * 16 * 32 * sizeof(float);
     auto kern = latent_attention_mma_kernel<NT>;
-    if (smem > 48 * 1024)
+    if (smem > 48 * 1024) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        const bool first = dev >= 0 && dev < kMaxDevices && !smem_done[dev];
         if (int e = ensure_dynamic_smem(kern, (int)smem, smem_done)) return e;
+        // all of the SM's unified memory as shared memory: three blocks of the rank-512 kernel then fit one SM
+        if (first) cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+    }
     const int groups = (n_heads + kMmaRows - 1) / kMmaRows;
     dim3 grid(n_tokens, groups, n_splits);
     cpm_launch(kLaunchAttention, kern, grid, 128, smem, stream, q, (const bf16*)cache, out, out_bf16, scratch, positions, token_seq, slots,

@@ -162,23 +162,23 @@ CPM_API int cpm_mingru_scan(const float* proj, const float* bz, const float* bx,
         if (n_seqs > 65535) return CPM_BAD_ARGUMENT;
         dim3 grid(bx_, n_seqs);
         if (dtype == CPM_BF16)
-            cpm_launch(kLaunchOther, mingru_scan_seq_kernel<bf16>, grid, threads, 0, stream, proj, bz, bx, state, positions, cu_q,
+            cpm_launch(kLaunchNorm, mingru_scan_seq_kernel<bf16>, grid, threads, 0, stream, proj, bz, bx, state, positions, cu_q,
                        slots, (bf16*)out, width);
         else
-            cpm_launch(kLaunchOther, mingru_scan_seq_kernel<float>, grid, threads, 0, stream, proj, bz, bx, state, positions, cu_q,
+            cpm_launch(kLaunchNorm, mingru_scan_seq_kernel<float>, grid, threads, 0, stream, proj, bz, bx, state, positions, cu_q,
                        slots, (float*)out, width);
         return launch_status();
     }
     if (n_tiles <= 0) return CPM_OK;
     if (n_tiles > 65535 || tile_tokens <= 0 || summary == nullptr) return CPM_BAD_ARGUMENT;
     dim3 grid(bx_, n_tiles);
-    cpm_launch(kLaunchOther, mingru_tile_summary_kernel, grid, threads, 0, stream, proj, bz, bx, (const float*)state, positions,
+    cpm_launch(kLaunchNorm, mingru_tile_summary_kernel, grid, threads, 0, stream, proj, bz, bx, (const float*)state, positions,
                cu_q, slots, tile_seq, tile_row, summary, width, tile_tokens);
     if (dtype == CPM_BF16)
-        cpm_launch(kLaunchOther, mingru_tile_apply_kernel<bf16>, grid, threads, 0, stream, proj, bz, bx, state, cu_q, slots,
+        cpm_launch(kLaunchNorm, mingru_tile_apply_kernel<bf16>, grid, threads, 0, stream, proj, bz, bx, state, cu_q, slots,
                    tile_seq, tile_row, (const float*)summary, (bf16*)out, width, tile_tokens);
     else
-        cpm_launch(kLaunchOther, mingru_tile_apply_kernel<float>, grid, threads, 0, stream, proj, bz, bx, state, cu_q, slots,
+        cpm_launch(kLaunchNorm, mingru_tile_apply_kernel<float>, grid, threads, 0, stream, proj, bz, bx, state, cu_q, slots,
                    tile_seq, tile_row, (const float*)summary, (float*)out, width, tile_tokens);
     return launch_status();
 }
