@@ -64,9 +64,10 @@ CPM_API int cpm_latent_norm_store(const float* proj, const float* wq, const floa
 constexpr int kProjectTokens = 8;      // tokens of one head that share a pass over the head's matrix
 constexpr int kProjectCols = 32;       // output columns of a block
 constexpr int kProjectParts = 8;       // parts of the sum over k, one per warp
+constexpr int kProjectFlight = 16;     // rows of the matrix a thread asks for before it uses the first
 
 // A block is 8 tokens x one head x 32 output columns; its eight warps split the sum over k (a warp reads 32
-// consecutive columns of every eighth row of the head's matrix, four rows in flight) and add up through shared memory.
+// consecutive columns of every eighth row of the head's matrix, sixteen rows in flight) and add up through shared memory.
 template <typename In, typename Wt, typename Out>
 __global__ void __launch_bounds__(kProjectCols * kProjectParts)
 head_project_kernel(const In* __restrict__ in, const Wt* __restrict__ w, Out* __restrict__ out,
@@ -90,12 +91,12 @@ head_project_kernel(const In* __restrict__ in, const Wt* __restrict__ w, Out* __
 #pragma unroll
     for (int tt = 0; tt < kProjectTokens; ++tt) acc[tt] = 0.f;
     int k = kp;
-    for (; k + 3 * kProjectParts < K; k += 4 * kProjectParts) {
-        float wv[4];
+    for (; k + (kProjectFlight - 1) * kProjectParts < K; k += kProjectFlight * kProjectParts) {
+        float wv[kProjectFlight];
 #pragma unroll
-        for (int u = 0; u < 4; ++u) wv[u] = to_f32(wh[(int64_t)(k + u * kProjectParts) * N]);
+        for (int u = 0; u < kProjectFlight; ++u) wv[u] = to_f32(wh[(int64_t)(k + u * kProjectParts) * N]);
 #pragma unroll
-        for (int u = 0; u < 4; ++u)
+        for (int u = 0; u < kProjectFlight; ++u)
 #pragma unroll
             for (int tt = 0; tt < kProjectTokens; ++tt) acc[tt] = fmaf(hp_smem[tt * K + k + u * kProjectParts], wv[u], acc[tt]);
     }
@@ -558,7 +559,14 @@ __global__ void latent_attention_merge_kernel(const float* __restrict__ scratch,
     const int64_t o = ((int64_t)t * n_heads + h) * rank;
     for (int c = threadIdx.x; c < rank; c += blockDim.x) {
         float acc = 0.f;
-        for (int s = 0; s < n_splits; ++s) acc = fmaf(base[s * share + c], weight[s], acc);
+        for (int s0 = 0; s0 < n_splits; s0 += 8) {
+            float v[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) v[u] = s0 + u < n_splits ? base[(s0 + u) * share + c] : 0.f;
+#pragma unroll
+            for (int u = 0; u < 8; ++u)
+                if (s0 + u < n_splits) acc = fmaf(v[u], weight[s0 + u], acc);
+        }
         const float res = acc * inv_l;
         if (out_bf16) static_cast<bf16*>(out_any)[o + c] = __float2bfloat16_rn(res);
         else static_cast<float*>(out_any)[o + c] = res;
