@@ -11,7 +11,7 @@
 //                       the query latent goes on as an activation, the key-value latent into the cache pages
 //   head_project        out[t, h, :] = in[t, h, :] @ w[h]   (w [heads][k][n]; fp32 accumulation), the per-head
 //                       maps Uk^T (queries into the latent space) and Uv (weighted latents into values)
-//   latent_attention    softmax attention of [tokens, heads, rank] fp32 queries over the latent pages; scores,
+//   latent_attention    softmax attention of [tokens, heads, rank] fp32 queries over the latent pages (rank up to 1,024); scores,
 //                       softmax and the weighted sum are fp32; a block is one token and up to 16 heads, which share
 //                       every tile of 32 latent rows through shared memory
 //
@@ -248,7 +248,7 @@ CPM_API int cpm_latent_attention(const float* q, const void* cache, float* out, 
                                  const int* slots, const int* page_table, int max_pages, int window, int n_tokens, int n_heads,
                                  int rank, float scale, int dtype, cudaStream_t stream) {
     if (n_tokens <= 0) return CPM_OK;
-    if (n_heads <= 0 || rank <= 0 || rank > 512 || window < 0) return CPM_BAD_ARGUMENT;
+    if (n_heads <= 0 || rank <= 0 || rank > 1024 || window < 0) return CPM_BAD_ARGUMENT;
 #define CPM_LATENT(RL)                                                                                                        \
     return dtype == CPM_BF16                                                                                                  \
         ? launch_latent_attention<bf16, RL>(q, cache, out, positions, token_seq, slots, page_table, max_pages, window,       \
@@ -258,7 +258,8 @@ CPM_API int cpm_latent_attention(const float* q, const void* cache, float* out, 
     if (rank <= 64) { CPM_LATENT(2); }
     if (rank <= 128) { CPM_LATENT(4); }
     if (rank <= 256) { CPM_LATENT(8); }
-    CPM_LATENT(16);
+    if (rank <= 512) { CPM_LATENT(16); }
+    CPM_LATENT(32);
 #undef CPM_LATENT
 }
 

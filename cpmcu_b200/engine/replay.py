@@ -29,7 +29,10 @@ def run(model_dir: str, dtype: str, out_dir: str, max_tokens: int, stdin: IO[str
         device: str = "cuda:0", chunk_tokens: int = 2048) -> int:
     os.makedirs(out_dir, exist_ok=True)
     _, config, model = load_model(model_dir, parse_dtype(dtype), device)
-    cache = Cache(model.cache_needs(), max_tokens=max_tokens, dtype=model.ops.dtype, device=device,
+    # ``max_tokens`` counts tokens; the cache hands out whole pages, and every live request's last page is partly
+    # empty: room for that is added for up to 256 requests at a time (or one per token, if that is fewer)
+    slack = min(int(max_tokens), 256) * PAGE_TOKENS
+    cache = Cache(model.cache_needs(), max_tokens=int(max_tokens) + slack, dtype=model.ops.dtype, device=device,
                   max_step_tokens=chunk_tokens)
     stepper = Stepper(model, cache, chunk_tokens=chunk_tokens)
     slots: Dict[str, int] = {}
@@ -69,7 +72,7 @@ def main(argv=None) -> int:
     p.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
     p.add_argument("--out", required=True, help="folder the logits files are written to")
     p.add_argument("--max-tokens", type=int, required=True,
-                   help="most tokens live requests hold at any time (each rounded up to 64); sizes the cache")
+                   help="most tokens live requests hold at any time; sizes the cache (room for partly filled pages is added)")
     p.add_argument("--chunk-tokens", type=int, default=2048, help="most packed tokens one forward pass takes")
     p.add_argument("--device", default="cuda:0")
     a = p.parse_args(argv)

@@ -35,8 +35,8 @@ class LatentAttention(Mixer):
         self.q_rank, self.kv_rank = int(q_rank), int(kv_rank)
         self.scale, self.eps = float(softmax_scale), float(eps)
         self.window = int(window) if window else 0
-        if self.kv_rank > 512:
-            raise ValueError(f"latent_attention: kv_rank {self.kv_rank} is beyond the 512 the attention kernel keeps per head")
+        if self.kv_rank > 1024:
+            raise ValueError(f"latent_attention: kv_rank {self.kv_rank} is beyond the 1,024 the attention kernels keep per head")
         self.names = dict(self.DEFAULT_NAMES, **(dict(names) if names else {}))
         self.w_down = self.w_uq = self.w_uk = self.w_uv = self.w_o = self.g_q = self.g_kv = None
 

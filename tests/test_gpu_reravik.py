@@ -277,6 +277,25 @@ def test_command_line_and_replay(folders, tmp_path):
     check(got2, want[[29]], "float32", "replay")
 
 
+def test_replay_of_many_short_requests_in_a_cache_sized_by_their_tokens(folders, tmp_path):
+    """Twenty requests of three and four tokens in one batch, then one more token each, with ``--max-tokens`` set to the
+    tokens they hold together: every request fills a small part of a page of its own."""
+    folder, cfg, w = folders("c")
+    reqs = [cases.random_ids(cfg["vocab"], 4 + (i % 2), 200 + i) for i in range(20)]
+    steps = [{"step": 0, "entries": [{"id": f"q{i}", "tokens": r[:-1], "want": [len(r) - 2]} for i, r in enumerate(reqs)], "end": []},
+             {"step": 1, "entries": [{"id": f"q{i}", "tokens": r[-1:], "want": [0]} for i, r in enumerate(reqs)],
+              "end": [f"q{i}" for i in range(20)]}]
+    out = tmp_path / "out"
+    p = subprocess.run([os.path.join(ROOT, "bin", "trace_run"), "--model", folder, "--dtype", "bfloat16", "--out", str(out),
+                        "--max-tokens", str(sum(len(r) for r in reqs))], input="\n".join(json.dumps(s) for s in steps) + "\n",
+                       capture_output=True, text=True, env=dict(os.environ, PYTHONPATH=ROOT), cwd=ROOT, timeout=600)
+    assert p.returncode == 0, p.stderr[-2000:]
+    for step, at in ((0, -2), (1, -1)):
+        got = torch.from_numpy(np.fromfile(out / f"{step}.f32", dtype="<f4")).view(20, -1)
+        want = torch.stack([plain_logits(cfg, w, r, "c")[at] for r in reqs])
+        check(got, want, "bfloat16", f"replay step {step}")
+
+
 # ---------------------------------------------------------------------------
 # mechanisms alone
 # ---------------------------------------------------------------------------
@@ -415,7 +434,7 @@ def test_embedding_gate_and_head_maps(dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("rank,window", [(48, 37), (72, 64), (160, 65), (512, 0)])
+@pytest.mark.parametrize("rank,window", [(48, 37), (72, 64), (160, 65), (512, 0), (600, 130)])
 def test_latent_attention_sees_exactly_its_window(dtype, rank, window):
     """Crafted latents: all rows are small but one, whose score towers over the others.  Placed just inside the
     window (the oldest visible key), just outside it, far back, at the first and last row of a page and at the
