@@ -57,7 +57,19 @@ def config_c() -> dict:
             ]}
 
 
-CONFIGS = {"a": config_a, "b": config_b, "c": config_c}
+def config_d() -> dict:
+    """Sizes that fit no kernel's favourite multiple: a width of 100, ranks of 50 and 40, seven heads of 20 with values
+    of 12, a recurrent width of 36, a feed-forward of 52, a window of five, one layer run four times."""
+    return {"architecture": NAME, "vocab": 77, "width": 100, "embedding": {"scale": 7.0}, "norm": {"eps": 1e-4},
+            "layers": [
+                {"type": "mingru", "mixer": {"width": 36}, "mlp": {"kind": "dense", "ff": 52}},
+                {"type": "latent_attention", "mixer": _latent(7, 20, 12, 50, 40, 0.22, 5), "mlp": {"kind": "dense", "ff": 52}},
+                {"type": "mingru", "mixer": {"width": 44}, "mlp": None},
+            ],
+            "loop": {"start": 1, "stop": 2, "times": 4}}
+
+
+CONFIGS = {"a": config_a, "b": config_b, "c": config_c, "d": config_d}
 
 
 def tensor_shapes(cfg: dict) -> Dict[str, tuple]:

@@ -105,7 +105,7 @@ def check(got, want, dtype, what=""):
 # ---------------------------------------------------------------------------
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name", ["a", "b", "c"])
+@pytest.mark.parametrize("name", ["a", "b", "c", "d"])
 def test_whole_prompt(folders, name, dtype):
     folder, cfg, w = folders(name)
     ids = cases.random_ids(cfg["vocab"], 150, 1)
@@ -118,7 +118,7 @@ def test_whole_prompt(folders, name, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name", ["a", "b"])
+@pytest.mark.parametrize("name", ["a", "b", "d"])
 def test_prompt_then_token_by_token_across_pages_and_windows(folders, name, dtype):
     """A prompt of 50 tokens, then 150 single tokens: the decoded tokens cross the page borders at 64, 128 and 192
     and, in configuration a, the edges of windows of 37 and 70 keys, inside a page and across one."""
