@@ -59,7 +59,7 @@ class CacheGroup:
             # holds beyond the sequence's end, and that has to be a finite number
             self.k = make("pages", (n, n_pages, needs.kv_heads, PAGE_TOKENS, needs.head_dim), dtype, True)
             if needs.values:      # a lane of shared latents keeps one row per token, and no transposed twin
-                self.v = make("pages", (n, n_pages, needs.kv_heads, needs.head_dim, PAGE_TOKENS), dtype, True)
+                self.v = make("pages", (n, n_pages, needs.kv_heads, needs.value_dim or needs.head_dim, PAGE_TOKENS), dtype, True)
             if needs.pooled_stride > 0:
                 if PAGE_TOKENS % needs.pooled_stride:
                     raise ValueError(f"pooled-key stride {needs.pooled_stride} must divide the page size {PAGE_TOKENS}")
@@ -71,7 +71,8 @@ class CacheGroup:
     def bytes_per_token(self) -> int:
         if self.k is None:
             return 0
-        per = (2 if self.needs.values else 1) * self.needs.kv_heads * self.needs.head_dim * self.k.element_size() * len(self.lanes)
+        row = self.needs.head_dim + ((self.needs.value_dim or self.needs.head_dim) if self.needs.values else 0)
+        per = row * self.needs.kv_heads * self.k.element_size() * len(self.lanes)
         if self.pooled is not None:
             per += self.needs.kv_heads * self.needs.head_dim * 4 * len(self.lanes) // self.needs.pooled_stride
         return per

@@ -228,7 +228,7 @@ CPM_API int cpm_silu_mul(const void* gu, void* h, int n_tokens, int inter, int i
 // fp32 with the accurate sincosf (src/model/rotary.cuh:6-34 uses the same pairing
 // but the fast-math cos/sin).  cos and sin are multiplied by ``magnitude`` (the
 // LongRoPE attention factor).  inv_freq == nullptr: no rotation.
-// qkv row: [heads*d | kv_heads*d | kv_heads*d].
+// qkv row: [heads*d | kv_heads*d | kv_heads*dv]; dv, the size of a value head, may differ from d.
 // ---------------------------------------------------------------------------
 constexpr int kRopeHeadsPerBlock = 4;
 
@@ -238,14 +238,14 @@ __global__ void rope_store_kernel(const T* __restrict__ qkv, T* __restrict__ q_o
                                   const int* __restrict__ positions, const int* __restrict__ token_seq,
                                   const int* __restrict__ slots, const int* __restrict__ page_table,
                                   int max_pages, const float* __restrict__ inv_freq, float magnitude,
-                                  int n_heads, int n_kv, int d, int rot_dim) {
+                                  int n_heads, int n_kv, int d, int rot_dim, int dv) {
     extern __shared__ float cs_table[];       // cos[half], sin[half] of this token
     pdl_launch_dependents();
     pdl_wait();
     const int t = blockIdx.x;
     const int pos = positions[t];
     const int half = rot_dim >> 1;
-    const int64_t row_stride = (int64_t)(n_heads + 2 * n_kv) * d;
+    const int64_t row_stride = (int64_t)(n_heads + n_kv) * d + (int64_t)n_kv * dv;
     const T* row = qkv + t * row_stride;
     const int n_all = n_heads + (k_cache ? 2 * n_kv : 0);       // q heads, then k heads, then v heads
     const int h_begin = blockIdx.y * kRopeHeadsPerBlock;
@@ -270,15 +270,16 @@ __global__ void rope_store_kernel(const T* __restrict__ qkv, T* __restrict__ q_o
         const int slot = slots[token_seq[t]];
         const int page = CPM_PAGE(page_table + (int64_t)slot * max_pages, pos / kPageTokens, max_pages);
         k_base = page_row_offset(page, 0, pos % kPageTokens, n_kv, d);
-        v_base = value_offset(page, 0, 0, pos % kPageTokens, n_kv, d);
+        v_base = value_offset(page, 0, 0, pos % kPageTokens, n_kv, dv);
     }
     const int64_t head_stride_in_page = (int64_t)kPageTokens * d;
     for (int h = h_begin; h < h_end; ++h) {
         const T* src = row + (int64_t)h * d;
         if (h >= n_heads + n_kv) {                               // a value head: transposed store
             const int kvh = h - n_heads - n_kv;
-            for (int c = threadIdx.x; c < d; c += blockDim.x)
-                v_cache[v_base + ((int64_t)kvh * d + c) * kPageTokens] = src[c];
+            src = row + (int64_t)(n_heads + n_kv) * d + (int64_t)kvh * dv;
+            for (int c = threadIdx.x; c < dv; c += blockDim.x)
+                v_cache[v_base + ((int64_t)kvh * dv + c) * kPageTokens] = src[c];
             continue;
         }
         T* dst = h < n_heads ? q_out + ((int64_t)t * n_heads + h) * d
@@ -381,15 +382,16 @@ __global__ void rope_store_vec_kernel(const bf16* __restrict__ qkv, bf16* __rest
     }
 }
 
-CPM_API int cpm_rope_store(const void* qkv, void* q_out, void* k_cache, void* v_cache, const int* positions,
-                           const int* token_seq, const int* slots, const int* page_table, int max_pages,
-                           const float* inv_freq, float magnitude, int n_tokens, int n_heads, int n_kv, int d,
-                           int rot_dim, int dtype, cudaStream_t stream) {
+// ``dv``: the size of a value head (the value pages are [kv_head][dv][token]).
+CPM_API int cpm_rope_store_dv(const void* qkv, void* q_out, void* k_cache, void* v_cache, const int* positions,
+                              const int* token_seq, const int* slots, const int* page_table, int max_pages,
+                              const float* inv_freq, float magnitude, int n_tokens, int n_heads, int n_kv, int d,
+                              int dv, int rot_dim, int dtype, cudaStream_t stream) {
     if (n_tokens <= 0) return CPM_OK;
-    if (rot_dim < 0 || rot_dim > d || (rot_dim & 1)) return CPM_BAD_ARGUMENT;
+    if (rot_dim < 0 || rot_dim > d || (rot_dim & 1) || dv < 1) return CPM_BAD_ARGUMENT;
     if ((k_cache == nullptr) != (v_cache == nullptr)) return CPM_BAD_ARGUMENT;
     const int n_all = n_heads + (k_cache ? 2 * n_kv : 0);
-    if (dtype == CPM_BF16 && rot_dim == d && d % 16 == 0 && d >= 16 && ((uintptr_t)qkv & 15) == 0 && ((uintptr_t)q_out & 15) == 0 &&
+    if (dtype == CPM_BF16 && rot_dim == d && dv == d && d % 16 == 0 && d >= 16 && ((uintptr_t)qkv & 15) == 0 && ((uintptr_t)q_out & 15) == 0 &&
         ((uintptr_t)k_cache & 15) == 0) {
         const int heads_per_block = n_tokens >= 64 ? n_all : kRopeHeadsPerBlock;
         const int items = heads_per_block * (d / 16);
@@ -407,11 +409,19 @@ CPM_API int cpm_rope_store(const void* qkv, void* q_out, void* k_cache, void* v_
     const size_t smem = (size_t)(rot_dim > 0 ? rot_dim : 2) * sizeof(float);
     if (dtype == CPM_BF16)
         cpm_launch(kLaunchRope, rope_store_kernel<bf16>, grid, threads, smem, stream, (const bf16*)qkv, (bf16*)q_out, (bf16*)k_cache,
-            (bf16*)v_cache, positions, token_seq, slots, page_table, max_pages, inv_freq, magnitude, n_heads, n_kv, d, rot_dim);
+            (bf16*)v_cache, positions, token_seq, slots, page_table, max_pages, inv_freq, magnitude, n_heads, n_kv, d, rot_dim, dv);
     else
         cpm_launch(kLaunchRope, rope_store_kernel<float>, grid, threads, smem, stream, (const float*)qkv, (float*)q_out, (float*)k_cache,
-            (float*)v_cache, positions, token_seq, slots, page_table, max_pages, inv_freq, magnitude, n_heads, n_kv, d, rot_dim);
+            (float*)v_cache, positions, token_seq, slots, page_table, max_pages, inv_freq, magnitude, n_heads, n_kv, d, rot_dim, dv);
     return launch_status();
+}
+
+CPM_API int cpm_rope_store(const void* qkv, void* q_out, void* k_cache, void* v_cache, const int* positions,
+                           const int* token_seq, const int* slots, const int* page_table, int max_pages,
+                           const float* inv_freq, float magnitude, int n_tokens, int n_heads, int n_kv, int d,
+                           int rot_dim, int dtype, cudaStream_t stream) {
+    return cpm_rope_store_dv(qkv, q_out, k_cache, v_cache, positions, token_seq, slots, page_table, max_pages, inv_freq,
+                             magnitude, n_tokens, n_heads, n_kv, d, d, rot_dim, dtype, stream);
 }
 
 // ---------------------------------------------------------------------------

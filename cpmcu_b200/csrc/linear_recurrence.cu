@@ -1,0 +1,366 @@
+// Linear recurrences with a matrix state per head (gated linear attention, gated delta rule).
+//
+// Per head the state S is [d, dv] (key channels x value channels), fp32, carried from token to token for each
+// sequence and kept in a per-sequence tensor [slots, heads, d, dv] (zeros at position 0).  One step:
+//
+//   S <- diag(a_t) S                a_t: one number per key channel, or one per head
+//   u  = v_t                        (plain form)
+//   u  = beta_t (v_t - S^T k_t)     (delta rule: what is stored under k_t is moved toward v_t)
+//   S <- S + k_t u^T
+//   o_t = S^T q_t * q_scale         (the read-out sees the current token's write)
+//
+// Every value column of S is independent of the others, so a column belongs to kLanes threads that split the
+// key channels among them (registers), and a block holds kCols columns of one head and sequence and walks the
+// sequence's tokens of the step.  Query and key head of value head h: h / (heads / qk_heads).
+//
+// Around it: the short causal convolution over time with SiLU, the unit-length scaling of q and k, the gates of
+// the delta rule, the decay of the gated linear attention, and the per-head RMS norm of the read-out times the
+// output gate.  All of it fp32; only the last kernel's output has the storage type.
+#include "common.cuh"
+
+__device__ __forceinline__ float sigmoid_acc(float v) { return 1.0f / (1.0f + expf(-v)); }
+__device__ __forceinline__ float silu_acc(float v) { return v / (1.0f + expf(-v)); }
+// log(1 + e^v) without overflow
+__device__ __forceinline__ float softplus_acc(float v) { return fmaxf(v, 0.f) + log1pf(expf(-fabsf(v))); }
+
+constexpr int kLanes = 8;      // threads that share one value column
+constexpr int kCols = 32;      // value columns per block
+
+template <int PER, bool DELTA, bool VECTOR_DECAY>
+__global__ void __launch_bounds__(kLanes * kCols)
+linear_recurrence_kernel(const float* __restrict__ q, const float* __restrict__ k, int64_t qk_stride,      // [tokens, qk_heads, d]
+                         const float* __restrict__ v, int64_t v_stride,                                    // [tokens, heads, dv]
+                         const float* __restrict__ decay, int64_t decay_stride,                            // [tokens, heads(, d)]
+                         const float* __restrict__ beta, int64_t beta_stride,                              // [tokens, heads]
+                         float* __restrict__ state, const int* __restrict__ positions, const int* __restrict__ cu_q,
+                         const int* __restrict__ slots, float* __restrict__ out,                           // [tokens, heads, dv]
+                         int heads, int qk_heads, int d, int dv, float q_scale) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int lane = threadIdx.x % kLanes;
+    const int col = blockIdx.x * kCols + threadIdx.x / kLanes;
+    const int h = blockIdx.y, seq = blockIdx.z;
+    const int t0 = cu_q[seq], t1 = cu_q[seq + 1];
+    if (t1 <= t0) return;
+    const bool live = col < dv;
+    const int colc = live ? col : dv - 1;
+    const int g = h / (heads / qk_heads);
+    float* st = state + (((int64_t)slots[seq] * heads + h) * d) * dv + colc;
+    const bool fresh = positions[t0] == 0;
+    float S[PER];
+#pragma unroll
+    for (int i = 0; i < PER; ++i) {
+        const int c = lane + kLanes * i;
+        S[i] = (c < d && !fresh) ? st[(int64_t)c * dv] : 0.f;
+    }
+    float kk[PER], qq[PER], aa[PER], vv, bb = 1.f, a1 = 1.f;
+    auto fetch = [&](int t) {
+        const float* kr = k + t * qk_stride + (int64_t)g * d;
+        const float* qr = q + t * qk_stride + (int64_t)g * d;
+#pragma unroll
+        for (int i = 0; i < PER; ++i) {
+            const int c = lane + kLanes * i;
+            kk[i] = c < d ? kr[c] : 0.f;
+            qq[i] = c < d ? qr[c] : 0.f;
+            if (VECTOR_DECAY) aa[i] = c < d ? decay[t * decay_stride + (int64_t)h * d + c] : 1.f;
+        }
+        if (!VECTOR_DECAY) a1 = decay[t * decay_stride + h];
+        vv = v[t * v_stride + (int64_t)h * dv + colc];
+        if (DELTA) bb = beta[t * beta_stride + h];
+    };
+    fetch(t0);
+    for (int t = t0; t < t1; ++t) {
+        float ck[PER], cq[PER], ca[PER];
+        const float cv = vv, cb = bb, c1 = a1;
+#pragma unroll
+        for (int i = 0; i < PER; ++i) {
+            ck[i] = kk[i];
+            cq[i] = qq[i];
+            ca[i] = VECTOR_DECAY ? aa[i] : c1;
+        }
+        if (t + 1 < t1) fetch(t + 1);              // the next token's operands are on their way while this one is worked
+        float u = cv;
+        if (DELTA) {
+            float dot = 0.f;
+#pragma unroll
+            for (int i = 0; i < PER; ++i) {
+                S[i] *= ca[i];
+                dot = fmaf(S[i], ck[i], dot);
+            }
+            dot += __shfl_xor_sync(0xffffffffu, dot, 1);
+            dot += __shfl_xor_sync(0xffffffffu, dot, 2);
+            dot += __shfl_xor_sync(0xffffffffu, dot, 4);
+            u = cb * (cv - dot);
+        } else {
+#pragma unroll
+            for (int i = 0; i < PER; ++i) S[i] *= ca[i];
+        }
+        float o = 0.f;
+#pragma unroll
+        for (int i = 0; i < PER; ++i) {
+            S[i] = fmaf(ck[i], u, S[i]);
+            o = fmaf(S[i], cq[i], o);
+        }
+        o += __shfl_xor_sync(0xffffffffu, o, 1);
+        o += __shfl_xor_sync(0xffffffffu, o, 2);
+        o += __shfl_xor_sync(0xffffffffu, o, 4);
+        if (lane == 0 && live) out[((int64_t)t * heads + h) * dv + col] = o * q_scale;
+    }
+    if (live) {
+#pragma unroll
+        for (int i = 0; i < PER; ++i) {
+            const int c = lane + kLanes * i;
+            if (c < d) st[(int64_t)c * dv] = S[i];
+        }
+    }
+}
+
+template <int PER>
+static void launch_recurrence(bool delta, bool vector_decay, dim3 grid, cudaStream_t stream, const float* q, const float* k,
+                              int64_t qk_stride, const float* v, int64_t v_stride, const float* decay, int64_t decay_stride,
+                              const float* beta, int64_t beta_stride, float* state, const int* positions, const int* cu_q,
+                              const int* slots, float* out, int heads, int qk_heads, int d, int dv, float q_scale) {
+    const dim3 block(kLanes * kCols);
+#define CPM_REC(D, V) cpm_launch(kLaunchAttention, linear_recurrence_kernel<PER, D, V>, grid, block, 0, stream, q, k, qk_stride, v, \
+                                 v_stride, decay, decay_stride, beta, beta_stride, state, positions, cu_q, slots, out, heads,      \
+                                 qk_heads, d, dv, q_scale)
+    if (delta && vector_decay) CPM_REC(true, true);
+    else if (delta) CPM_REC(true, false);
+    else if (vector_decay) CPM_REC(false, true);
+    else CPM_REC(false, false);
+#undef CPM_REC
+}
+
+// q, k: fp32 rows of ``qk_stride`` floats holding [qk_heads, d]; v: rows of ``v_stride`` floats holding [heads, dv];
+// decay: rows of ``decay_stride`` floats holding [heads, d] (vector_decay) or [heads]; beta: rows holding [heads], or
+// null for the plain form.  state [slots, heads, d, dv] fp32.  out [tokens, heads, dv] fp32.
+CPM_API int cpm_linear_recurrence(const float* q, const float* k, int64_t qk_stride, const float* v, int64_t v_stride,
+                                  const float* decay, int64_t decay_stride, int vector_decay, const float* beta,
+                                  int64_t beta_stride, float* state, const int* positions, const int* cu_q, const int* slots,
+                                  float* out, int n_seqs, int heads, int qk_heads, int d, int dv, float q_scale,
+                                  cudaStream_t stream) {
+    if (n_seqs <= 0) return CPM_OK;
+    if (heads < 1 || qk_heads < 1 || heads % qk_heads || d < 1 || dv < 1 || d > kLanes * 32) return CPM_BAD_ARGUMENT;
+    const dim3 grid((dv + kCols - 1) / kCols, heads, n_seqs);
+    const bool delta = beta != nullptr;
+#define CPM_REC_PER(P) launch_recurrence<P>(delta, vector_decay != 0, grid, stream, q, k, qk_stride, v, v_stride, decay, decay_stride, \
+                                            beta, beta_stride, state, positions, cu_q, slots, out, heads, qk_heads, d, dv, q_scale)
+    const int per = (d + kLanes - 1) / kLanes;
+    if (per <= 4) CPM_REC_PER(4);
+    else if (per <= 8) CPM_REC_PER(8);
+    else if (per <= 16) CPM_REC_PER(16);
+    else CPM_REC_PER(32);
+#undef CPM_REC_PER
+    return launch_status();
+}
+
+// ---------------------------------------------------------------------------
+// Short causal convolution over time, SiLU, unit length, and the delta rule's gates.
+//
+// proj rows (fp32, ``stride`` floats) begin with [q: qk_heads*d | k: qk_heads*d | v: heads*dv]; these C channels each
+// pass y_t = sum_j taps[c][K-1-j] x_(t-j) (zeros before the sequence's start) and SiLU.  The K-1 inputs before a
+// step's first token come from conv_state [slots, K-1, C] (oldest first).  q and k heads are then scaled to unit
+// length, x / sqrt(sum x^2 + unit_eps).  One warp per (token, head of q, k or v).  For value head h the first lane
+// also forms beta = sigmoid(b_raw) and the decay exp(-exp(A_log[h]) * softplus(a_raw + dt_bias[h])) from the
+// columns ``b_col + h`` and ``a_col + h`` of the row.
+// ---------------------------------------------------------------------------
+constexpr int kConvMaxPerLane = 8;      // head sizes up to 256
+constexpr int kConvMaxTaps = 8;
+
+__global__ void conv_prepare_kernel(const float* __restrict__ proj, int64_t stride, const float* __restrict__ taps,
+                                    const float* __restrict__ conv_state, const int* __restrict__ positions,
+                                    const int* __restrict__ token_seq, const int* __restrict__ cu_q,
+                                    const int* __restrict__ slots, float* __restrict__ qo, float* __restrict__ ko,
+                                    float* __restrict__ vo, float* __restrict__ beta, float* __restrict__ decay,
+                                    const float* __restrict__ a_log, const float* __restrict__ dt_bias, int b_col, int a_col,
+                                    int heads, int qk_heads, int d, int dv, int K, float unit_eps, int n_tokens) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int lane = threadIdx.x & 31;
+    const int units = 2 * qk_heads + heads;
+    const int64_t w = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (w >= (int64_t)n_tokens * units) return;
+    const int t = (int)(w / units), unit = (int)(w % units);
+    const int C = 2 * qk_heads * d + heads * dv;
+    int width, c0;
+    float* dst;
+    if (unit < qk_heads) { width = d; c0 = unit * d; dst = qo + ((int64_t)t * qk_heads + unit) * d; }
+    else if (unit < 2 * qk_heads) { width = d; c0 = unit * d; dst = ko + ((int64_t)t * qk_heads + unit - qk_heads) * d; }
+    else { width = dv; c0 = 2 * qk_heads * d + (unit - 2 * qk_heads) * dv; dst = vo + ((int64_t)t * heads + unit - 2 * qk_heads) * dv; }
+    const int seq = token_seq[t];
+    const int local = t - cu_q[seq], pos = positions[t];
+    const float* cs = conv_state + (int64_t)slots[seq] * (K - 1) * C;
+    float val[kConvMaxPerLane];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < kConvMaxPerLane; ++i) {
+        const int e = lane + 32 * i;
+        float acc = 0.f;
+        if (e < width) {
+            const int c = c0 + e;
+            for (int j = 0; j < K; ++j) {              // tap j reaches j tokens back
+                if (pos - j < 0) break;
+                const float x = local - j >= 0 ? proj[(int64_t)(t - j) * stride + c] : cs[(int64_t)(K - 1 + local - j) * C + c];
+                acc = fmaf(taps[(int64_t)c * K + K - 1 - j], x, acc);
+            }
+            acc = silu_acc(acc);
+        }
+        val[i] = acc;
+        ss = fmaf(acc, acc, ss);
+    }
+    float f = 1.f;
+    if (unit < 2 * qk_heads) f = 1.0f / sqrtf(warp_sum(ss) + unit_eps);
+#pragma unroll
+    for (int i = 0; i < kConvMaxPerLane; ++i) {
+        const int e = lane + 32 * i;
+        if (e < width) dst[e] = val[i] * f;
+    }
+    if (unit >= 2 * qk_heads && lane == 0) {
+        const int h = unit - 2 * qk_heads;
+        const float* row = proj + (int64_t)t * stride;
+        beta[(int64_t)t * heads + h] = sigmoid_acc(row[b_col + h]);
+        decay[(int64_t)t * heads + h] = expf(-expf(a_log[h]) * softplus_acc(row[a_col + h] + dt_bias[h]));
+    }
+}
+
+// The convolution's state after the step: for every sequence the last K-1 inputs, taken from the step's rows and,
+// where the step brought fewer, from the old state.  A thread owns a channel and reads all it needs before it
+// writes.  Runs after conv_prepare_kernel, which only reads the state.
+__global__ void conv_state_update_kernel(const float* __restrict__ proj, int64_t stride, float* __restrict__ conv_state,
+                                         const int* __restrict__ positions, const int* __restrict__ cu_q,
+                                         const int* __restrict__ slots, int C, int K) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    const int seq = blockIdx.y;
+    if (c >= C) return;
+    const int t0 = cu_q[seq], t1 = cu_q[seq + 1];
+    const int n = t1 - t0;
+    if (n <= 0) return;
+    const bool fresh = positions[t0] == 0;
+    float* cs = conv_state + (int64_t)slots[seq] * (K - 1) * C + c;
+    float keep[kConvMaxTaps];
+#pragma unroll
+    for (int i = 0; i < kConvMaxTaps; ++i) {
+        if (i < K - 1) {
+            const int back = K - 1 - i;                // entry i is the input ``back`` tokens before the next token
+            if (back <= n) keep[i] = proj[(int64_t)(t1 - back) * stride + c];
+            else keep[i] = fresh ? 0.f : cs[(int64_t)(i + n) * C];
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < kConvMaxTaps; ++i)
+        if (i < K - 1) cs[(int64_t)i * C] = keep[i];
+}
+
+CPM_API int cpm_conv_prepare(const float* proj, int64_t stride, const float* taps, float* conv_state, const int* positions,
+                             const int* token_seq, const int* cu_q, const int* slots, float* qo, float* ko, float* vo,
+                             float* beta, float* decay, const float* a_log, const float* dt_bias, int b_col, int a_col,
+                             int n_tokens, int n_seqs, int heads, int qk_heads, int d, int dv, int K, float unit_eps,
+                             cudaStream_t stream) {
+    if (n_tokens <= 0) return CPM_OK;
+    if (K < 1 || K > kConvMaxTaps || d > 32 * kConvMaxPerLane || dv > 32 * kConvMaxPerLane || heads < 1 || qk_heads < 1)
+        return CPM_BAD_ARGUMENT;
+    const int units = 2 * qk_heads + heads;
+    const int warps = 8;
+    const int64_t blocks = ((int64_t)n_tokens * units + warps - 1) / warps;
+    cpm_launch(kLaunchRope, conv_prepare_kernel, dim3((unsigned)blocks), dim3(warps * 32), 0, stream, proj, stride, taps,
+               (const float*)conv_state, positions, token_seq, cu_q, slots, qo, ko, vo, beta, decay, a_log, dt_bias, b_col, a_col,
+               heads, qk_heads, d, dv, K, unit_eps, n_tokens);
+    if (K > 1) {
+        const int C = 2 * qk_heads * d + heads * dv;
+        cpm_launch(kLaunchOther, conv_state_update_kernel, dim3((C + 127) / 128, n_seqs), dim3(128), 0, stream, proj, stride,
+                   conv_state, positions, cu_q, slots, C, K);
+    }
+    return launch_status();
+}
+
+// Decay of the gated linear attention, in place: z <- sigmoid(z + bias)^(1/tau) = exp(-softplus(-(z + bias)) / tau).
+__global__ void sigmoid_power_kernel(float* __restrict__ z, const float* __restrict__ bias, float inv_tau, int64_t n, int width) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const float v = z[i] + bias[i % width];
+    z[i] = expf(-softplus_acc(-v) * inv_tau);
+}
+
+CPM_API int cpm_sigmoid_power(float* z, const float* bias, float tau, int n_tokens, int width, cudaStream_t stream) {
+    if (n_tokens <= 0) return CPM_OK;
+    if (width < 1 || !(tau > 0.f)) return CPM_BAD_ARGUMENT;
+    const int64_t n = (int64_t)n_tokens * width;
+    cpm_launch(kLaunchOther, sigmoid_power_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, z, bias, 1.0f / tau, n, width);
+    return launch_status();
+}
+
+// out[t][h][:] = o[t][h][:] / sqrt(mean(o^2) + eps) * weight[:] * silu(gate[t][h][:]), one warp per (token, head);
+// o fp32 [tokens, heads, dv], gate fp32 rows of ``gate_stride`` floats holding [heads, dv], out in the storage type.
+template <typename T>
+__global__ void gated_head_norm_kernel(const float* __restrict__ o, const float* __restrict__ gate, int64_t gate_stride,
+                                       const float* __restrict__ weight, T* __restrict__ out, int heads, int dv, float eps,
+                                       int64_t n_units) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int lane = threadIdx.x & 31;
+    const int64_t w = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (w >= n_units) return;
+    const int64_t t = w / heads;
+    const int h = (int)(w % heads);
+    const float* row = o + w * dv;
+    float ss = 0.f;
+    for (int c = lane; c < dv; c += 32) ss = fmaf(row[c], row[c], ss);
+    const float f = rsqrtf(warp_sum(ss) / (float)dv + eps);
+    const float* gr = gate + t * gate_stride + (int64_t)h * dv;
+    for (int c = lane; c < dv; c += 32) out[w * dv + c] = from_f32<T>(row[c] * f * weight[c] * silu_acc(gr[c]));
+}
+
+CPM_API int cpm_gated_head_norm(const float* o, const float* gate, int64_t gate_stride, const float* weight, void* out,
+                                int n_tokens, int heads, int dv, float eps, int dtype, cudaStream_t stream) {
+    if (n_tokens <= 0) return CPM_OK;
+    if (heads < 1 || dv < 1) return CPM_BAD_ARGUMENT;
+    const int64_t units = (int64_t)n_tokens * heads;
+    const int warps = 8;
+    const dim3 grid((unsigned)((units + warps - 1) / warps));
+    if (dtype == CPM_BF16)
+        cpm_launch(kLaunchNorm, gated_head_norm_kernel<bf16>, grid, dim3(warps * 32), 0, stream, o, gate, gate_stride, weight, (bf16*)out,
+                   heads, dv, eps, units);
+    else
+        cpm_launch(kLaunchNorm, gated_head_norm_kernel<float>, grid, dim3(warps * 32), 0, stream, o, gate, gate_stride, weight,
+                   (float*)out, heads, dv, eps, units);
+    return launch_status();
+}
+
+// out = (rms(a) * wa + rms(b) * wb) / 2 over the model width: the join of two mixers that ran side by side.
+template <typename T>
+__global__ void dual_rmsnorm_mean_kernel(const T* __restrict__ a, const T* __restrict__ b, const float* __restrict__ wa,
+                                         const float* __restrict__ wb, T* __restrict__ out, int W, float eps) {
+    __shared__ float scratch[33];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int64_t t = blockIdx.x;
+    float sa = 0.f, sb = 0.f;
+    for (int c = threadIdx.x; c < W; c += blockDim.x) {
+        const float x = to_f32(a[t * W + c]), y = to_f32(b[t * W + c]);
+        sa = fmaf(x, x, sa);
+        sb = fmaf(y, y, sb);
+    }
+    sa = block_sum(sa, scratch);
+    sb = block_sum(sb, scratch);
+    const float fa = rsqrtf(sa / (float)W + eps), fb = rsqrtf(sb / (float)W + eps);
+    for (int c = threadIdx.x; c < W; c += blockDim.x)
+        out[t * W + c] = from_f32<T>(0.5f * (to_f32(a[t * W + c]) * fa * wa[c] + to_f32(b[t * W + c]) * fb * wb[c]));
+}
+
+CPM_API int cpm_dual_rmsnorm_mean(const void* a, const void* b, const float* wa, const float* wb, void* out, int n_tokens, int W,
+                                  float eps, int dtype, cudaStream_t stream) {
+    if (n_tokens <= 0) return CPM_OK;
+    if (W < 1) return CPM_BAD_ARGUMENT;
+    const dim3 block(W >= 1024 ? 256 : 128);
+    if (dtype == CPM_BF16)
+        cpm_launch(kLaunchNorm, dual_rmsnorm_mean_kernel<bf16>, dim3(n_tokens), block, 0, stream, (const bf16*)a, (const bf16*)b, wa, wb,
+                   (bf16*)out, W, eps);
+    else
+        cpm_launch(kLaunchNorm, dual_rmsnorm_mean_kernel<float>, dim3(n_tokens), block, 0, stream, (const float*)a, (const float*)b, wa,
+                   wb, (float*)out, W, eps);
+    return launch_status();
+}

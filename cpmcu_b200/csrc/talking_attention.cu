@@ -1,0 +1,159 @@
+// Causal softmax attention whose weights are mixed across heads after the softmax ("talking heads"), with a
+// learned temperature per head, over the paged cache.
+//
+//   s_g(i, j) = q_g(i) . k_kv(g)(j) * scale * temp[g]            j <= i
+//   p_g(i, :) = softmax_j s_g(i, :)
+//   w_h(i, j) = sum_g talk[h][g] p_g(i, j)
+//   o_h(i)    = sum_j w_h(i, j) v_kv(h)(j)
+//
+// The mix needs every head's *normalised* weight of a key, so a query is worked in two walks over its keys: the
+// first finds every head's maximum and sum, the second forms p_g for 32 keys at a time in shared memory, mixes
+// them and adds the values.  One block per query token, one warp per head; a lane owns a key in the scores and a
+// set of value channels in the weighted sum (value pages are [kv_head][dv][token], so 32 keys of a channel are
+// contiguous).  Scores, weights and sums are fp32; q, the cache and the output have the storage type.  Key size d
+// and value size dv are independent.
+#include "common.cuh"
+
+constexpr int kTalkMaxHeads = 32;
+constexpr int kTalkMaxVPerLane = 8;      // dv <= 256
+
+template <typename T>
+__device__ __forceinline__ float key_dot(const T* __restrict__ krow, const float* __restrict__ qs, int d) {
+    float dot = 0.f;
+    for (int c = 0; c < d; ++c) dot = fmaf(qs[c], to_f32(krow[c]), dot);
+    return dot;
+}
+
+template <>
+__device__ __forceinline__ float key_dot<bf16>(const bf16* __restrict__ krow, const float* __restrict__ qs, int d) {
+    float dot = 0.f;
+    if ((d & 7) == 0 && (((uintptr_t)krow) & 15) == 0) {
+        for (int c = 0; c < d; c += 8) {
+            const uint4 raw = *reinterpret_cast<const uint4*>(krow + c);
+            const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float2 f = __bfloat1622float2(h2[i]);
+                dot = fmaf(qs[c + 2 * i], f.x, dot);
+                dot = fmaf(qs[c + 2 * i + 1], f.y, dot);
+            }
+        }
+        return dot;
+    }
+    for (int c = 0; c < d; ++c) dot = fmaf(qs[c], __bfloat162float(krow[c]), dot);
+    return dot;
+}
+
+template <typename T>
+__global__ void talking_attention_kernel(const T* __restrict__ q,            // [tokens, heads, d]
+                                         const T* __restrict__ k_cache, const T* __restrict__ v_cache,
+                                         T* __restrict__ out,                // [tokens, heads, dv]
+                                         const int* __restrict__ positions, const int* __restrict__ token_seq,
+                                         const int* __restrict__ slots, const int* __restrict__ page_table, int max_pages,
+                                         const float* __restrict__ temp, const float* __restrict__ talk,
+                                         int n_heads, int n_kv, int d, int dv, float scale) {
+    extern __shared__ float smem[];
+    float* qs = smem;                               // [heads][d]
+    float* P = qs + n_heads * d;                    // [heads][32]
+    float* tk = P + n_heads * 32;                   // [heads][heads]
+    pdl_launch_dependents();
+    for (int i = threadIdx.x; i < n_heads * n_heads; i += blockDim.x) tk[i] = talk[i];
+    pdl_wait();
+    const int g = threadIdx.x >> 5, lane = threadIdx.x & 31;       // this warp's head
+    const int t = blockIdx.x;
+    const int p = positions[t];
+    const int* pages = page_table + (int64_t)slots[token_seq[t]] * max_pages;
+    const int kvh = g / (n_heads / n_kv);
+    const float s_scale = scale * temp[g];
+    {
+        const T* qrow = q + ((int64_t)t * n_heads + g) * d;
+        for (int c = lane; c < d; c += 32) qs[g * d + c] = to_f32(qrow[c]);
+    }
+    __syncthreads();
+    const float* qg = qs + g * d;
+
+    // first walk: this head's maximum and sum
+    float m = -INFINITY, l = 0.f;
+    for (int j0 = 0; j0 <= p; j0 += 32) {
+        const int j = j0 + lane;
+        if (j <= p) {
+            const int page = CPM_PAGE(pages, j / kPageTokens, max_pages);
+            const float s = key_dot(k_cache + page_row_offset(page, kvh, j % kPageTokens, n_kv, d), qg, d) * s_scale;
+            const float m_new = fmaxf(m, s);
+            l = l * expf(m - m_new) + expf(s - m_new);       // expf(-inf) = 0 at the first key
+            m = m_new;
+        }
+    }
+    const float M = warp_max(m);
+    const float L = warp_sum(m == -INFINITY ? 0.f : l * expf(m - M));
+    const float inv_L = 1.0f / L;
+
+    // second walk: normalised weights of 32 keys, mixed across heads, times the values
+    float acc[kTalkMaxVPerLane];
+#pragma unroll
+    for (int i = 0; i < kTalkMaxVPerLane; ++i) acc[i] = 0.f;
+    for (int j0 = 0; j0 <= p; j0 += 32) {
+        const int j = j0 + lane;
+        float pr = 0.f;
+        const int page0 = CPM_PAGE(pages, j0 / kPageTokens, max_pages);      // 32 keys from a multiple of 32 lie in one page
+        if (j <= p) {
+            const float s = key_dot(k_cache + page_row_offset(page0, kvh, j % kPageTokens, n_kv, d), qg, d) * s_scale;
+            pr = expf(s - M) * inv_L;
+        }
+        P[g * 32 + lane] = pr;
+        __syncthreads();
+        float w = 0.f;
+        for (int gg = 0; gg < n_heads; ++gg) w = fmaf(tk[g * n_heads + gg], P[gg * 32 + lane], w);
+        const int n_here = min(32, p + 1 - j0);
+        const T* vbase = v_cache + value_offset(page0, kvh, 0, j0 % kPageTokens, n_kv, dv);
+        for (int jj = 0; jj < n_here; ++jj) {
+            const float wj = __shfl_sync(0xffffffffu, w, jj);
+#pragma unroll
+            for (int i = 0; i < kTalkMaxVPerLane; ++i) {
+                const int c = lane + 32 * i;
+                if (c < dv) acc[i] = fmaf(wj, to_f32(vbase[(int64_t)c * kPageTokens + jj]), acc[i]);
+            }
+        }
+        __syncthreads();
+    }
+    T* orow = out + ((int64_t)t * n_heads + g) * dv;
+#pragma unroll
+    for (int i = 0; i < kTalkMaxVPerLane; ++i) {
+        const int c = lane + 32 * i;
+        if (c < dv) orow[c] = from_f32<T>(acc[i]);
+    }
+}
+
+static bool g_talk_smem_done_bf16[kMaxDevices], g_talk_smem_done_f32[kMaxDevices];
+
+CPM_API int cpm_talking_attention(const void* q, const void* k_cache, const void* v_cache, void* out, const int* positions,
+                                  const int* token_seq, const int* slots, const int* page_table, int max_pages,
+                                  const float* temp, const float* talk, int n_tokens, int n_heads, int n_kv, int d, int dv,
+                                  float scale, int dtype, cudaStream_t stream) {
+    if (n_tokens <= 0) return CPM_OK;
+    if (n_heads < 1 || n_heads > kTalkMaxHeads || n_kv < 1 || n_heads % n_kv || d < 1 || dv < 1 || dv > 32 * kTalkMaxVPerLane)
+        return CPM_BAD_ARGUMENT;
+    const size_t smem = (size_t)(n_heads * d + n_heads * 32 + n_heads * n_heads) * sizeof(float);
+    if (smem > 200 * 1024) return CPM_BAD_ARGUMENT;
+    const dim3 grid(n_tokens), block(32 * n_heads);
+    if (dtype == CPM_BF16) {
+        if (smem > 48 * 1024) {
+            const int e = ensure_dynamic_smem(talking_attention_kernel<bf16>, 200 * 1024, g_talk_smem_done_bf16);
+            if (e != CPM_OK) return e;
+        }
+        cpm_launch(kLaunchAttention, talking_attention_kernel<bf16>, grid, block, smem, stream, (const bf16*)q, (const bf16*)k_cache,
+                   (const bf16*)v_cache, (bf16*)out, positions, token_seq, slots, page_table, max_pages, temp, talk, n_heads, n_kv,
+                   d, dv, scale);
+    } else {
+        if (smem > 48 * 1024) {
+            const int e = ensure_dynamic_smem(talking_attention_kernel<float>, 200 * 1024, g_talk_smem_done_f32);
+            if (e != CPM_OK) return e;
+        }
+        cpm_launch(kLaunchAttention, talking_attention_kernel<float>, grid, block, smem, stream, (const float*)q,
+                   (const float*)k_cache, (const float*)v_cache, (float*)out, positions, token_seq, slots, page_table, max_pages,
+                   temp, talk, n_heads, n_kv, d, dv, scale);
+    }
+    return launch_status();
+}
+
+CPM_BOUNDS_TU(talking_attention)

@@ -99,6 +99,8 @@ class Model:
         if not ctx.extras.get("step_begun"):
             ops.begin_step()           # the caller did not lay out the step's workspace itself
         stream = ResidualStream(ops, self.embedding.forward(ctx.token_ids, ctx.positions))
+        if self.spec.streams:
+            stream.fan_out(self.spec.streams)      # in the step's persistent part, like the stream itself
         embedded = None
         if self.pass_entry is not None:
             # the stream as the embedding left it outlives the layers: it lies in the step's persistent part

@@ -60,11 +60,28 @@ _SIGNATURES = {
     "cpm_latent_norm_store": [_P, _P, _P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_float, c_int, _P],
     "cpm_head_project": [_P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P],
     "cpm_latent_attention": [_P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_float, c_int, _P],
+    "cpm_rope_store_dv": [_P, _P, _P, _P, _P, _P, _P, _P, c_int, _P, c_float, c_int, c_int, c_int, c_int, c_int, c_int,
+                          c_int, _P],
+    "cpm_hyper_step": [_P, _P, _P, _P, _P, _P, c_float, _P, _P, c_int, c_int, c_int, c_int, _P],
+    "cpm_hyper_fan_out": [_P, _P, c_int, c_int, c_int, _P],
+    "cpm_linear_recurrence": [_P, _P, c_int64, _P, c_int64, _P, c_int64, c_int, _P, c_int64, _P, _P, _P, _P, _P, c_int, c_int,
+                              c_int, c_int, c_int, c_float, _P],
+    "cpm_conv_prepare": [_P, c_int64, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int,
+                         c_int, c_int, c_int, c_int, c_float, _P],
+    "cpm_sigmoid_power": [_P, _P, c_float, c_int, c_int, _P],
+    "cpm_gated_head_norm": [_P, _P, c_int64, _P, _P, c_int, c_int, c_int, c_float, c_int, _P],
+    "cpm_dual_rmsnorm_mean": [_P, _P, _P, _P, _P, c_int, c_int, c_float, c_int, _P],
+    "cpm_talking_attention": [_P, _P, _P, _P, _P, _P, _P, _P, c_int, _P, _P, c_int, c_int, c_int, c_int, c_int, c_float, c_int, _P],
+    "cpm_moe_route": [_P, c_int, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, _P],
+    "cpm_moe_group": [_P, c_int, c_int, _P, _P, _P],
+    "cpm_moe_expert_product": [_P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P],
+    "cpm_moe_combine": [_P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, _P],
     "cpm_latent_attention_mma": [_P, _P, _P, c_int, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_float, c_int, _P],
 }
 
 # source files whose kernels follow page tables; the checked build (CPMCU_CHECK_BOUNDS=1) keeps a record per file
-BOUNDS_FILES = ("attention_bf16", "attention_generic", "attention_tcgen05", "elementwise", "latent_attention", "sparse")
+BOUNDS_FILES = ("attention_bf16", "attention_generic", "attention_tcgen05", "elementwise", "latent_attention", "sparse",
+                "talking_attention")
 
 _lock = threading.Lock()
 _lib: Optional[ctypes.CDLL] = None

@@ -730,6 +730,213 @@ class Ops:
             raise RuntimeError("block selection met a query with more candidate key blocks than the launch made room "
                                "for (a sequence longer than the bound the step gave); the results of this step are not valid")
 
+    # ---- several residual streams ----
+    def hyper_fan_out(self, x: torch.Tensor, n_streams: int) -> torch.Tensor:
+        """fp32 [tokens, hidden] -> fp32 [tokens, streams, hidden], every stream a copy of x."""
+        self._f32(x, "residual stream")
+        n, hidden = x.shape
+        X = self.empty(n, n_streams, hidden, dtype=torch.float32)
+        check(self.lib.cpm_hyper_fan_out(_ptr(x), _ptr(X), n, n_streams, hidden, self._stream()), "hyper_fan_out")
+        return X
+
+    def hyper_step(self, X: torch.Tensor, write=None, read=None, eps: float = 0.0, total: Optional[torch.Tensor] = None
+                   ) -> Optional[torch.Tensor]:
+        """One pass over the residual streams X fp32 [tokens, streams, hidden], in place.  ``write`` = (y, mix, out):
+        X_r <- sum_s mix[s][r] X_s + out[r] * y.  ``read`` = (in, gain): returns rms_norm(sum_s in[s] X_s) * gain in the
+        compute dtype.  ``total`` (fp32 [tokens, hidden]) receives the sum of the streams."""
+        self._f32(X, "residual streams")
+        n, S, hidden = X.shape
+        y = mix = out_w = in_w = gain = h = None
+        if write is not None:
+            y, mix, out_w = write
+            self._act(y, "sublayer output")
+            if y.shape != (n, hidden):
+                raise ValueError(f"sublayer output {tuple(y.shape)} does not match the streams {tuple(X.shape)}")
+            self._f32(mix, "stream mix")
+            self._f32(out_w, "stream output weights")
+        if read is not None:
+            in_w, gain = read
+            self._f32(in_w, "stream input weights")
+            self._f32(gain, "norm gain")
+            h = self.empty(n, hidden)
+        if total is not None:
+            self._f32(total, "sum of the streams")
+        check(self.lib.cpm_hyper_step(_ptr(X), _ptr(y), _ptr(mix), _ptr(out_w), _ptr(in_w), _ptr(gain), float(eps), _ptr(h),
+                                      _ptr(total), n, S, hidden, self.code, self._stream()), f"hyper_step ({S} streams)")
+        return h
+
+    # ---- linear recurrences with a matrix state ----
+    def linear_recurrence(self, ctx, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay: torch.Tensor,
+                          beta: Optional[torch.Tensor], state: torch.Tensor, heads: int, qk_heads: int, d: int, dv: int,
+                          q_scale: float, vector_decay: bool = False) -> torch.Tensor:
+        """S <- diag(decay) S; u = v (or beta (v - S^T k) when ``beta`` is given); S <- S + k u^T; o = S^T q * q_scale, per
+        head and token, in 32-bit.  q, k: fp32 views [tokens, qk_heads * d]; v: [tokens, heads * dv]; decay: [tokens, heads], or
+        with ``vector_decay`` [tokens, heads * d] (one number per key channel); beta: [tokens, heads]; rows may be slices of wider rows (unit
+        stride inside a row).  state fp32 [slots, heads, d, dv], read at a sequence's first token of the step (zeros at
+        position 0) and written at its last.  Returns fp32 [tokens, heads, dv]."""
+        n = q.shape[0]
+        for t, what, width in ((q, "q", qk_heads * d), (k, "k", qk_heads * d), (v, "v", heads * dv)):
+            if t.dtype != torch.float32 or t.shape != (n, width) or t.stride(1) != 1:
+                raise ValueError(f"linear_recurrence: {what} must be fp32 [tokens, {width}] with unit stride inside a row")
+        if q.stride(0) != k.stride(0):
+            raise ValueError("linear_recurrence: q and k must have the same row stride")
+        vector = bool(vector_decay)
+        if decay.shape != (n, heads * d if vector else heads) or decay.dtype != torch.float32 or decay.stride(1) != 1:
+            raise ValueError("linear_recurrence: decay must be fp32 [tokens, heads] or, with vector_decay, [tokens, heads * d]")
+        if beta is not None and (beta.dtype != torch.float32 or beta.shape != (n, heads) or beta.stride(1) != 1):
+            raise ValueError("linear_recurrence: beta must be fp32 [tokens, heads]")
+        self._f32(state, "recurrence state")
+        if tuple(state.shape[1:]) != (heads, d, dv):
+            raise ValueError(f"linear_recurrence: state {tuple(state.shape)} is not [slots, {heads}, {d}, {dv}]")
+        out = self.empty(n, heads, dv, dtype=torch.float32)
+        check(self.lib.cpm_linear_recurrence(_ptr(q), _ptr(k), q.stride(0), _ptr(v), v.stride(0), _ptr(decay), decay.stride(0),
+                                             1 if vector else 0, _ptr(beta), beta.stride(0) if beta is not None else 0,
+                                             _ptr(state), _ptr(ctx.positions), _ptr(ctx.cu_q), _ptr(ctx.slot_dev), _ptr(out),
+                                             ctx.n_seqs, heads, qk_heads, d, dv, float(q_scale), self._stream()),
+              f"linear_recurrence ({heads} heads, {d} x {dv})")
+        return out
+
+    def conv_prepare(self, ctx, proj: torch.Tensor, taps: torch.Tensor, conv_state: torch.Tensor, a_log: torch.Tensor,
+                     dt_bias: torch.Tensor, b_col: int, a_col: int, heads: int, qk_heads: int, d: int, dv: int, unit_eps: float):
+        """proj fp32 [tokens, N] whose rows begin [q | k | v] and hold the raw gates at columns ``b_col`` and ``a_col``
+        (one per head): short causal convolution (taps fp32 [channels, K], the last column the current token's) and SiLU
+        on q, k, v; q and k heads scaled to unit length; beta = sigmoid(b), decay = exp(-exp(a_log) softplus(a + dt_bias)).
+        conv_state fp32 [slots, K-1, channels] gives the inputs before the step and takes those after it.  Returns fp32
+        (q [tokens, qk_heads*d], k, v [tokens, heads*dv], beta [tokens, heads], decay [tokens, heads])."""
+        self._f32(proj, "projections")
+        self._f32(taps, "convolution taps")
+        self._f32(conv_state, "convolution state")
+        n = proj.shape[0]
+        C, K = taps.shape
+        if C != 2 * qk_heads * d + heads * dv or tuple(conv_state.shape[1:]) != (max(K - 1, 1), C):
+            raise ValueError("conv_prepare: taps [channels, K] and state [slots, K-1, channels] do not match the head sizes")
+        qo = self.empty(n, qk_heads * d, dtype=torch.float32)
+        ko = self.empty(n, qk_heads * d, dtype=torch.float32)
+        vo = self.empty(n, heads * dv, dtype=torch.float32)
+        beta = self.empty(n, heads, dtype=torch.float32)
+        decay = self.empty(n, heads, dtype=torch.float32)
+        check(self.lib.cpm_conv_prepare(_ptr(proj), proj.stride(0), _ptr(taps), _ptr(conv_state), _ptr(ctx.positions),
+                                        _ptr(ctx.token_seq), _ptr(ctx.cu_q), _ptr(ctx.slot_dev), _ptr(qo), _ptr(ko), _ptr(vo),
+                                        _ptr(beta), _ptr(decay), _ptr(a_log), _ptr(dt_bias), int(b_col), int(a_col), n, ctx.n_seqs,
+                                        heads, qk_heads, d, dv, K, float(unit_eps), self._stream()), "conv_prepare")
+        if K > 1:
+            LAUNCHES_EXTRA[0] += 1
+        return qo, ko, vo, beta, decay
+
+    def sigmoid_power(self, z: torch.Tensor, bias: torch.Tensor, tau: float) -> torch.Tensor:
+        """In place on fp32 [tokens, width]: sigmoid(z + bias)^(1/tau)."""
+        self._f32(z, "decay logits")
+        self._f32(bias, "decay bias")
+        check(self.lib.cpm_sigmoid_power(_ptr(z), _ptr(bias), float(tau), z.shape[0], z.shape[1], self._stream()), "sigmoid_power")
+        return z
+
+    def gated_head_norm(self, o: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
+        """o fp32 [tokens, heads, dv], gate fp32 [tokens, heads*dv] (may be a slice of wider rows), weight fp32 [dv] ->
+        rms_norm(o) * weight * silu(gate) per head, [tokens, heads*dv] in the compute dtype."""
+        self._f32(o, "recurrence output")
+        self._f32(weight, "head norm weight")
+        n, heads, dv = o.shape
+        if gate.dtype != torch.float32 or gate.shape != (n, heads * dv) or gate.stride(1) != 1:
+            raise ValueError("gated_head_norm: the gate must be fp32 [tokens, heads*dv]")
+        out = self.empty(n, heads * dv)
+        check(self.lib.cpm_gated_head_norm(_ptr(o), _ptr(gate), gate.stride(0), _ptr(weight), _ptr(out), n, heads, dv, float(eps),
+                                           self.code, self._stream()), "gated_head_norm")
+        return out
+
+    def dual_rmsnorm_mean(self, a: torch.Tensor, b: torch.Tensor, wa: torch.Tensor, wb: torch.Tensor, eps: float) -> torch.Tensor:
+        """(rms_norm(a) * wa + rms_norm(b) * wb) / 2 over the last axis, [tokens, hidden] in the compute dtype."""
+        self._act(a, "left output")
+        self._act(b, "right output")
+        self._f32(wa, "left norm weight")
+        self._f32(wb, "right norm weight")
+        if a.shape != b.shape:
+            raise ValueError("dual_rmsnorm_mean: the two outputs differ in shape")
+        out = self.empty(*a.shape)
+        check(self.lib.cpm_dual_rmsnorm_mean(_ptr(a), _ptr(b), _ptr(wa), _ptr(wb), _ptr(out), a.shape[0], a.shape[1], float(eps),
+                                             self.code, self._stream()), "dual_rmsnorm_mean")
+        return out
+
+    # ---- attention with weights mixed across heads ----
+    def rope_store_dv(self, ctx, qkv: torch.Tensor, lane, n_heads: int, n_kv: int, d: int, dv: int,
+                      inv_freq: Optional[torch.Tensor], rot_dim: int, write_cache: bool = True) -> torch.Tensor:
+        """qkv [tokens, heads*d + kv*d + kv*dv]: rotates q and k (the first ``rot_dim`` dimensions of a head, pairs
+        (i, i + rot_dim/2)), stores k and v into the lane's pages, returns the rotated q [tokens, heads, d]."""
+        self._act(qkv, "qkv")
+        n = qkv.shape[0]
+        if qkv.shape[1] != (n_heads + n_kv) * d + n_kv * dv:
+            raise ValueError("qkv row size does not match the head counts")
+        q = self.empty(n, n_heads, d)
+        check(self.lib.cpm_rope_store_dv(_ptr(qkv), _ptr(q), _ptr(lane.k) if write_cache else None,
+                                         _ptr(lane.v) if write_cache else None, _ptr(ctx.positions), _ptr(ctx.token_seq),
+                                         _ptr(ctx.slot_dev), _ptr(lane.page_table), lane.page_table.shape[1], _ptr(inv_freq), 1.0,
+                                         n, n_heads, n_kv, d, dv, int(rot_dim), self.code, self._stream()), "rope_store_dv")
+        return q
+
+    def talking_attention(self, ctx, q: torch.Tensor, lane, n_kv: int, dv: int, scale: float, temp: torch.Tensor,
+                          talk: torch.Tensor) -> torch.Tensor:
+        """Causal softmax attention over the lane's cache with scores times ``scale * temp[head]`` and the softmax
+        weights mixed across heads by ``talk`` [heads, heads] (row: the head that receives); q [tokens, heads, d] ->
+        [tokens, heads*dv]."""
+        self._act(q, "q")
+        self._f32(temp, "head temperatures")
+        self._f32(talk, "head mix")
+        n, n_heads, d = q.shape
+        out = self.empty(n, n_heads * dv)
+        check(self.lib.cpm_talking_attention(_ptr(q), _ptr(lane.k), _ptr(lane.v), _ptr(out), _ptr(ctx.positions),
+                                             _ptr(ctx.token_seq), _ptr(ctx.slot_dev), _ptr(lane.page_table),
+                                             lane.page_table.shape[1], _ptr(temp), _ptr(talk), n, n_heads, n_kv, d, dv,
+                                             float(scale), self.code, self._stream()),
+              f"talking-heads attention ({n_heads} heads, {d} / {dv})")
+        return out
+
+    # ---- routed experts ----
+    def moe_route(self, logits: torch.Tensor, correction: torch.Tensor, n_experts: int, top: int, n_groups: int, keep: int,
+                  gate_col: int = -1):
+        """logits fp32 [tokens, >= experts] -> (chosen int32 [tokens, top], weights fp32 [tokens, top], sigmoid of column
+        ``gate_col`` fp32 [tokens] or None)."""
+        self._f32(logits, "router logits")
+        self._f32(correction, "router correction")
+        n = logits.shape[0]
+        chosen = self.empty(n, top, dtype=torch.int32)
+        weights = self.empty(n, top, dtype=torch.float32)
+        gate = self.empty(n, dtype=torch.float32) if gate_col >= 0 else None
+        check(self.lib.cpm_moe_route(_ptr(logits), logits.shape[1], _ptr(correction), _ptr(chosen), _ptr(weights), _ptr(gate),
+                                     int(gate_col), n, n_experts, top, n_groups, keep, self._stream()),
+              f"moe_route ({n_experts} experts, top {top})")
+        return chosen, weights, gate
+
+    def moe_experts(self, x: torch.Tensor, chosen: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor,
+                    w_down: torch.Tensor) -> torch.Tensor:
+        """x [tokens, hidden]; chosen int32 [tokens, top]; stacks w_gate, w_up [experts, ff, hidden], w_down [experts,
+        hidden, ff] -> every pair's expert output, [tokens * top, hidden] in the compute dtype."""
+        self._act(x, "expert input")
+        for w, what in ((w_gate, "gate stack"), (w_up, "up stack"), (w_down, "down stack")):
+            self._act(w, what)
+        n, hidden = x.shape
+        top = chosen.shape[1]
+        E, ff, _ = w_gate.shape
+        pairs = n * top
+        offsets = self.empty(E + 1, dtype=torch.int32)
+        order = self.empty(pairs, dtype=torch.int32)
+        check(self.lib.cpm_moe_group(_ptr(chosen), pairs, E, _ptr(offsets), _ptr(order), self._stream()), "moe_group")
+        h = self.empty(pairs, ff)
+        check(self.lib.cpm_moe_expert_product(_ptr(x), _ptr(w_gate), _ptr(w_up), _ptr(h), _ptr(offsets), _ptr(order), pairs, E, top,
+                                              ff, hidden, 1, self.code, self._stream()), "moe gate/up product")
+        y = self.empty(pairs, hidden)
+        check(self.lib.cpm_moe_expert_product(_ptr(h), _ptr(w_down), None, _ptr(y), _ptr(offsets), _ptr(order), pairs, E, top,
+                                              hidden, ff, 0, self.code, self._stream()), "moe down product")
+        return y
+
+    def moe_combine(self, y: torch.Tensor, weights: torch.Tensor, shared: Optional[torch.Tensor],
+                    gate: Optional[torch.Tensor]) -> torch.Tensor:
+        """out[t] = sum_k weights[t][k] * y[t*top + k] (+ gate[t] * shared[t])."""
+        n, top = weights.shape
+        hidden = y.shape[1]
+        out = self.empty(n, hidden)
+        check(self.lib.cpm_moe_combine(_ptr(y), _ptr(weights), _ptr(shared), _ptr(gate), _ptr(out), n, top, hidden, self.code,
+                                       self._stream()), "moe_combine")
+        return out
+
     # ---- the checked build (CPMCU_CHECK_BOUNDS=1) ----
     def set_page_limit(self, n_pages: int) -> None:
         """Tells the checked kernels how many pages the cache in use holds (no-op in the ordinary build)."""

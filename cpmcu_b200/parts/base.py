@@ -121,6 +121,10 @@ class ModelSpec:
     # are named below ``pass_entry_name``.
     pass_entry: Optional[PartSpec] = None
     pass_entry_name: str = ""
+    # Residual streams per token (0: the one plain stream).  With streams every token carries that many copies of the
+    # residual vector, all equal to the embedding's output at the start; blocks that know of them read and write
+    # ``ResidualStream.copies``, and the model's output norm sees their sum.
+    streams: int = 0
 
     def n_lanes(self) -> int:
         return 1 + max(e.lane for e in self.schedule)
@@ -152,7 +156,7 @@ class CacheNeeds:
     most recent tokens that do.  pooled_stride/pooled_kernel: an extra row per
     ``pooled_stride`` tokens (mean-pooled keys); 0 = none.  values: False when the
     lane keeps key rows only (a shared latent that keys and values are both made
-    from).  state: tensors of fixed size per sequence, name -> (shape, dtype); they
+    from).  value_dim: the size of a value row where it differs from a key row's (0: the same).  state: tensors of fixed size per sequence, name -> (shape, dtype); they
     are zero when a sequence starts.
     """
 
@@ -163,9 +167,10 @@ class CacheNeeds:
     pooled_kernel: int = 0
     state: Mapping[str, Tuple[Tuple[int, ...], torch.dtype]] = field(default_factory=dict)
     values: bool = True
+    value_dim: int = 0
 
     def group_key(self) -> Tuple:
-        return (self.kv_heads, self.head_dim, self.window, self.pooled_stride, self.pooled_kernel, self.values)
+        return (self.kv_heads, self.head_dim, self.window, self.pooled_stride, self.pooled_kernel, self.values, self.value_dim)
 
     def with_state(self, more: Mapping[str, Tuple[Tuple[int, ...], torch.dtype]]) -> "CacheNeeds":
         """The same needs with further per-sequence tensors (a block adds its own to its mixer's)."""
@@ -174,7 +179,8 @@ class CacheNeeds:
             if name in both:
                 raise ValueError(f"per-sequence state '{name}' is declared twice for one lane")
             both[name] = what
-        return CacheNeeds(self.kv_heads, self.head_dim, self.window, self.pooled_stride, self.pooled_kernel, both, self.values)
+        return CacheNeeds(self.kv_heads, self.head_dim, self.window, self.pooled_stride, self.pooled_kernel, both, self.values,
+                          self.value_dim)
 
 
 # ---------------------------------------------------------------------------
@@ -266,6 +272,15 @@ class ResidualStream:
         self.x = x
         self.pending: Optional[torch.Tensor] = None
         self.pending_scale: float = 1.0
+        # several streams per token: fp32 [tokens, streams, hidden], and the last sublayer's write still to be done
+        # (its output, the mix matrix, the output weights), which the next read performs in the same pass
+        self.copies: Optional[torch.Tensor] = None
+        self.pending_write = None
+
+    def fan_out(self, n_streams: int) -> None:
+        """From here on the token carries ``n_streams`` residual vectors, each a copy of x."""
+        self.flush()
+        self.copies = self.ops.hyper_fan_out(self.x, int(n_streams))
 
     def add(self, delta: torch.Tensor, scale: float = 1.0) -> None:
         self.flush()
@@ -273,12 +288,19 @@ class ResidualStream:
         self.pending_scale = float(scale)
 
     def flush(self) -> torch.Tensor:
+        if self.copies is not None:
+            # x becomes the sum of the streams (after the write that is still due)
+            self.ops.hyper_step(self.copies, write=self.pending_write, total=self.x)
+            self.pending_write = None
+            return self.x
         if self.pending is not None:
             self.ops.residual_add(self.x, self.pending, self.pending_scale)
             self.pending = None
         return self.x
 
     def normed(self, norm: Norm, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+        if self.copies is not None:
+            return norm.forward(self.flush(), rows)
         if self.pending is None:
             return norm.forward(self.x, rows)
         y = norm.add_forward(self.x, self.pending, self.pending_scale, rows)

@@ -96,3 +96,65 @@ class SandwichNormShiftBlock(Block):
         y = self.post_mixer_norm.add_normed(x, a, then=self.feed_forward_norm)
         f = self.feed_forward.forward(ctx, y)
         self.post_feed_forward_norm.add_normed(x, f)
+
+
+@BLOCKS.register("hyper_connections")
+class HyperConnectionsBlock(Block):
+    """A layer over several residual streams per token.  Sublayer q (1: mixer, 2: feed-forward) reads one blend of the
+    streams and writes into all of them:
+
+        u = sum_s in_q[s] x_s;   y = sublayer_q(norm_q(u));   x_r <- sum_s mix_q[s][r] x_s + out_q[r] y   (all r at once)
+
+    with the layer's tensors ``<names["hyper1"]>in`` [S], ``...out`` [S], ``...mix`` [S, S] (indexed [from][to]), and the
+    same under ``names["hyper2"]``.  The norms are RMS norms with one number (``scalar_rms_norm``); the streams and
+    everything here are 32-bit.  A sublayer's write is done by the kernel of the next read (of this layer's second
+    sublayer, or of the next layer's first), which also norms; the model's output norm sees the sum of the streams.
+    """
+
+    recordable_prompt = True
+
+    def __init__(self, ops, mixer, feed_forward, mixer_norm, feed_forward_norm, names, n_streams: int):
+        super().__init__(ops, mixer, feed_forward, mixer_norm, feed_forward_norm, names)
+        self.n_streams = int(n_streams)
+        for n in (mixer_norm, feed_forward_norm):
+            if n is not None and not hasattr(n, "gain"):
+                raise ValueError("hyper_connections needs norms with one gain (scalar_rms_norm)")
+        self.hyper = {}
+
+    def _subs(self):
+        return ["hyper1"] + (["hyper2"] if self.feed_forward is not None else [])
+
+    def weight_specs(self) -> Dict[str, WeightSpec]:
+        out = super().weight_specs()
+        S = self.n_streams
+        for sub in self._subs():
+            p = self.names.get(sub, sub + ".")
+            out[p + "in"] = WeightSpec((S,), "vector")
+            out[p + "out"] = WeightSpec((S,), "vector")
+            out[p + "mix"] = WeightSpec((S, S), "vector")
+        return out
+
+    def load_weights(self, tensors: Dict[str, torch.Tensor]) -> None:
+        super().load_weights(tensors)
+        for sub in self._subs():
+            p = self.names.get(sub, sub + ".")
+            self.hyper[sub] = tuple(self.ops.keep(tensors[p + k].float().contiguous()) for k in ("in", "out", "mix"))
+
+    def weight_bytes(self) -> int:
+        return super().weight_bytes() + len(self._subs()) * 4 * (2 * self.n_streams + self.n_streams ** 2)
+
+    def forward(self, ctx, stream: ResidualStream, lane, writes_cache: bool) -> None:
+        X = stream.copies
+        if X is None or X.shape[1] != self.n_streams:
+            raise ValueError(f"hyper_connections: the model carries no {self.n_streams} residual streams (ModelSpec.streams)")
+        ops = self.ops
+        in1, out1, mix1 = self.hyper["hyper1"]
+        h = ops.hyper_step(X, write=stream.pending_write, read=(in1, self.mixer_norm.gain), eps=self.mixer_norm.eps)
+        a = self.mixer.forward(ctx, h, lane, writes_cache)
+        stream.pending_write = (a, mix1, out1)
+        if self.feed_forward is None:
+            return
+        in2, out2, mix2 = self.hyper["hyper2"]
+        h2 = ops.hyper_step(X, write=stream.pending_write, read=(in2, self.feed_forward_norm.gain), eps=self.feed_forward_norm.eps)
+        f = self.feed_forward.forward(ctx, h2)
+        stream.pending_write = (f, mix2, out2)

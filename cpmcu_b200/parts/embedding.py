@@ -21,16 +21,18 @@ HEADS: Registry[Type[Part]] = Registry("output head")
 class ScaledEmbedding(Part):
     recordable_prompt = True
 
-    def __init__(self, ops, vocab_size: int, hidden_size: int, scale: float = 1.0):
+    def __init__(self, ops, vocab_size: int, hidden_size: int, scale: float = 1.0, weight_name: str = "weight"):
         super().__init__(ops)
         self.vocab_size, self.hidden_size, self.scale = int(vocab_size), int(hidden_size), float(scale)
+        self.weight_name = str(weight_name)      # the table's name below the part's prefix
         self.weight: Optional[torch.Tensor] = None
 
     def weight_specs(self) -> Dict[str, WeightSpec]:
-        return {"weight": WeightSpec((self.vocab_size, self.hidden_size))}
+        return {self.weight_name: WeightSpec((self.vocab_size, self.hidden_size))}
 
     def load_weights(self, tensors: Dict[str, torch.Tensor]) -> None:
-        self.weight = self.ops.keep(tensors["weight"].contiguous()) if self.ops is not None else tensors["weight"]
+        w = tensors[self.weight_name]
+        self.weight = self.ops.keep(w.contiguous()) if self.ops is not None else w
 
     def forward(self, token_ids: torch.Tensor, positions: Optional[torch.Tensor] = None) -> torch.Tensor:
         return self.ops.embed(token_ids, self.weight, self.scale)

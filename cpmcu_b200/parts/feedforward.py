@@ -64,3 +64,83 @@ class GatedFeedForward(FeedForward):
     def forward(self, ctx, y: torch.Tensor) -> torch.Tensor:
         h = self.ops.gated_linear(y, self.w_gate_up, self.interleave, self.activation)
         return self.ops.linear(h, self.w_down)
+
+
+@FEED_FORWARDS.register("routed_experts")
+class RoutedExperts(FeedForward):
+    """A mixture of gated feed-forward experts, of which every token uses ``top``:
+
+        s = softmax(W_router y)  (32-bit);  choice scores c = s + correction
+        experts form ``n_groups`` equal groups of neighbours; a group's score is its largest c; only experts of the
+        ``keep_groups`` best groups can be chosen; the ``top`` largest c among them are chosen
+        out = sum over the chosen e of s_e * down_e( act(gate_e y) * up_e y )            (s_e not renormalised)
+            + sigmoid(w_sg . y) * shared(y)                                              (when ``shared_size`` > 0)
+
+    Expert e's matrices are ``<names["expert"]><e>.gate`` / ``.up`` / ``.down``; the shared expert's lie under
+    ``names["shared"]`` with its gate vector ``names["shared_gate"]`` [1, hidden].  The router's product (with the
+    shared gate's row appended) has 32-bit results; the experts' products run over the (token, expert) pairs grouped
+    by expert, on the device, with no host read.
+    """
+
+    recordable_prompt = True
+    DEFAULT_NAMES = {"router": "router", "correction": "correction", "expert": "e", "gate": ".gate", "up": ".up", "down": ".down",
+                     "shared": "shared.", "shared_gate": "shared.sg"}
+
+    def __init__(self, ops, hidden_size: int, n_experts: int, top: int, expert_size: int, n_groups: int = 1, keep_groups: int = 1,
+                 shared_size: int = 0, names=None):
+        super().__init__(ops)
+        self.hidden_size, self.E, self.top, self.ff = int(hidden_size), int(n_experts), int(top), int(expert_size)
+        self.n_groups, self.keep = int(n_groups), int(keep_groups)
+        if self.E % self.n_groups or not 1 <= self.keep <= self.n_groups:
+            raise ValueError(f"routed_experts: {self.E} experts do not form {self.n_groups} equal groups of which {self.keep} are kept")
+        if not 1 <= self.top <= self.keep * (self.E // self.n_groups):
+            raise ValueError(f"routed_experts: top {self.top} exceeds the experts of the kept groups")
+        if self.E > 512:
+            raise ValueError("routed_experts: the routing kernel takes up to 512 experts")
+        self.names = dict(self.DEFAULT_NAMES, **(dict(names) if names else {}))
+        self.shared = None
+        if shared_size:
+            self.shared = GatedFeedForward(ops, hidden_size, shared_size, "silu",
+                                           {"gate": "gate", "up": "up", "down": "down"})
+
+    def _expert(self, e: int, which: str) -> str:
+        return f"{self.names['expert']}{e}{self.names[which]}"
+
+    def weight_specs(self) -> Dict[str, WeightSpec]:
+        n, W, ff = self.names, self.hidden_size, self.ff
+        out = {n["router"]: WeightSpec((self.E, W)), n["correction"]: WeightSpec((self.E,), "vector")}
+        for e in range(self.E):
+            out[self._expert(e, "gate")] = WeightSpec((ff, W))
+            out[self._expert(e, "up")] = WeightSpec((ff, W))
+            out[self._expert(e, "down")] = WeightSpec((W, ff))
+        if self.shared is not None:
+            for name, spec in self.shared.weight_specs().items():
+                out[n["shared"] + name] = spec
+            out[n["shared_gate"]] = WeightSpec((1, W))
+        return out
+
+    def load_weights(self, tensors: Dict[str, torch.Tensor]) -> None:
+        n = self.names
+        rows = [tensors[n["router"]]] + ([tensors[n["shared_gate"]]] if self.shared is not None else [])
+        self.w_router = self.ops.keep(torch.cat(rows, dim=0).contiguous())
+        self.correction = self.ops.keep(tensors[n["correction"]].float().contiguous())
+        self.w_gate = self.ops.keep(torch.stack([tensors[self._expert(e, "gate")] for e in range(self.E)]).contiguous())
+        self.w_up = self.ops.keep(torch.stack([tensors[self._expert(e, "up")] for e in range(self.E)]).contiguous())
+        self.w_down = self.ops.keep(torch.stack([tensors[self._expert(e, "down")] for e in range(self.E)]).contiguous())
+        if self.shared is not None:
+            self.shared.load_weights({name: tensors[n["shared"] + name] for name in self.shared.weight_specs()})
+
+    def weight_bytes(self) -> int:
+        """What a decode step of one token reads: the router, ``top`` experts, the shared expert."""
+        per_expert = 3 * self.ff * self.hidden_size * self.w_gate.element_size()
+        total = self.w_router.numel() * self.w_router.element_size() + self.top * per_expert
+        return total + (self.shared.weight_bytes() if self.shared is not None else 0)
+
+    def forward(self, ctx, y: torch.Tensor) -> torch.Tensor:
+        ops = self.ops
+        logits = ops.linear(y, self.w_router, out_f32=True)
+        chosen, weights, gate = ops.moe_route(logits, self.correction, self.E, self.top, self.n_groups, self.keep,
+                                              gate_col=self.E if self.shared is not None else -1)
+        pairs = ops.moe_experts(y, chosen, self.w_gate, self.w_up, self.w_down)
+        shared = self.shared.forward(ctx, y) if self.shared is not None else None
+        return ops.moe_combine(pairs, weights, shared, gate)

@@ -1,0 +1,149 @@
+"""Mixers whose memory is a matrix per head that every token decays and adds to (a linear recurrence), instead of
+cached keys.  Per head S is [d, dv], 32-bit, zero at a sequence's start, kept per sequence by the cache manager:
+
+    S <- diag(a_t) S;   u = v_t  or  beta_t (v_t - S^T k_t);   S <- S + k_t u^T;   o_t = S^T q_t
+
+The projections come from one product with 32-bit results; everything after them (convolution, activations, unit
+lengths, gates, decays, the recurrence, the per-head norm) is 32-bit; the gated, normed read-out enters the output
+projection in the compute dtype.
+"""
+from __future__ import annotations
+
+from typing import Dict, Optional
+
+import torch
+
+from .base import MIXERS, CacheNeeds, Mixer, WeightSpec
+
+
+class _MatrixStateMixer(Mixer):
+    recordable_prompt = True
+
+    def _keep32(self, t: torch.Tensor) -> torch.Tensor:
+        return self.ops.keep(t.float().contiguous())
+
+    def cache_bytes_read(self, kv_len: int) -> int:
+        return 4 * self.heads * self.d * self.dv
+
+
+@MIXERS.register("gated_linear_attention")
+class GatedLinearAttention(_MatrixStateMixer):
+    """Linear attention with a decay per key channel:
+
+        q = Wq h * d^(-1/2),  k = Wk h,  v = Wv h,  a = sigmoid(Wa2 (Wa1 h) + ba2)^(1/tau)      (a: heads x d)
+        S_t = diag(a_t) S_(t-1) + k_t v_t^T,   o_t = S_t^T q_t
+        out = Wo ( rms_norm_dv(o) * w_norm * silu(Wg h) )                                        (norm per head)
+
+    ``names``: tensors below the part's prefix by "q", "k", "v", "g", "o", "norm", "a1", "a2", "a2_bias".
+    """
+
+    DEFAULT_NAMES = {"q": "q", "k": "k", "v": "v", "g": "g", "o": "o", "norm": "norm", "a1": "a1", "a2": "a2", "a2_bias": "a2.b"}
+
+    def __init__(self, ops, hidden_size: int, n_heads: int, head_dim: int, value_dim: int, decay_rank: int, tau: float,
+                 eps: float, names=None):
+        super().__init__(ops)
+        self.hidden_size, self.heads, self.d, self.dv = int(hidden_size), int(n_heads), int(head_dim), int(value_dim)
+        self.rank, self.tau, self.eps = int(decay_rank), float(tau), float(eps)
+        self.names = dict(self.DEFAULT_NAMES, **(dict(names) if names else {}))
+
+    def weight_specs(self) -> Dict[str, WeightSpec]:
+        n, W, H, d, dv, r = self.names, self.hidden_size, self.heads, self.d, self.dv, self.rank
+        return {n["q"]: WeightSpec((H * d, W)), n["k"]: WeightSpec((H * d, W)), n["v"]: WeightSpec((H * dv, W)),
+                n["g"]: WeightSpec((H * dv, W)), n["o"]: WeightSpec((W, H * dv)), n["norm"]: WeightSpec((dv,), "vector"),
+                n["a1"]: WeightSpec((r, W)), n["a2"]: WeightSpec((H * d, r)), n["a2_bias"]: WeightSpec((H * d,), "vector")}
+
+    def load_weights(self, tensors: Dict[str, torch.Tensor]) -> None:
+        n = self.names
+        self.w_in = self.ops.keep(torch.cat([tensors[n[x]] for x in ("q", "k", "v", "g")], dim=0).contiguous())
+        self.w_a1 = self.ops.keep(tensors[n["a1"]].contiguous())
+        self.w_a2 = self.ops.keep(tensors[n["a2"]].contiguous())
+        self.w_o = self.ops.keep(tensors[n["o"]].contiguous())
+        self.b_a2 = self._keep32(tensors[n["a2_bias"]])
+        self.w_norm = self._keep32(tensors[n["norm"]])
+
+    def weight_bytes(self) -> int:
+        return sum(t.numel() * t.element_size() for t in (self.w_in, self.w_a1, self.w_a2, self.w_o, self.b_a2, self.w_norm))
+
+    def cache_needs(self) -> CacheNeeds:
+        return CacheNeeds(state={"matrix_state": ((self.heads, self.d, self.dv), torch.float32)})
+
+    def forward(self, ctx, y: torch.Tensor, lane, writes_cache: bool) -> torch.Tensor:
+        ops, H, d, dv = self.ops, self.heads, self.d, self.dv
+        proj = ops.linear(y, self.w_in, out_f32=True)                       # [q | k | v | g]
+        z = ops.linear(ops.linear(y, self.w_a1), self.w_a2, out_f32=True)
+        decay = ops.sigmoid_power(z, self.b_a2, self.tau)
+        q, k = proj[:, :H * d], proj[:, H * d:2 * H * d]
+        v, g = proj[:, 2 * H * d:2 * H * d + H * dv], proj[:, 2 * H * d + H * dv:]
+        o = ops.linear_recurrence(ctx, q, k, v, decay, None, lane.state["matrix_state"], H, H, d, dv, d ** -0.5,
+                                  vector_decay=True)
+        return ops.linear(ops.gated_head_norm(o, g, self.w_norm, self.eps), self.w_o)
+
+
+@MIXERS.register("gated_delta_rule")
+class GatedDeltaRule(_MatrixStateMixer):
+    """The gated delta rule with short convolutions:
+
+        q, k, v = silu(conv(Wq h)), silu(conv(Wk h)), silu(conv(Wv h))      conv: causal over time, per channel, K taps
+        q, k <- unit length per head (x / sqrt(sum x^2 + 1e-6));  q <- q * d^(-1/2)
+        beta = sigmoid(Wb h);   g = exp(-exp(A_log) * softplus(Wa h + dt_bias))                  (one per head)
+        S <- g S;   u = beta (v - S^T k);   S <- S + k u^T;   o = S^T q
+        out = Wo ( rms_norm_dv(o) * w_norm * silu(Wg h) )
+
+    q and k have ``n_qk_heads`` heads; value head h uses q/k head h / (heads / qk_heads).  Besides S the last K-1
+    inputs of the convolutions are per-sequence state.  ``names``: "q", "k", "v" (their taps under ``<name>.conv``),
+    "b", "a", "A_log", "dt_bias", "g", "o", "norm".
+    """
+
+    DEFAULT_NAMES = {"q": "q", "k": "k", "v": "v", "conv": ".conv", "b": "b", "a": "a", "A_log": "A_log", "dt_bias": "dt_bias",
+                     "g": "g", "o": "o", "norm": "norm"}
+    UNIT_EPS = 1e-6
+
+    def __init__(self, ops, hidden_size: int, n_heads: int, n_qk_heads: int, head_dim: int, value_dim: int, conv_taps: int,
+                 eps: float, names=None):
+        super().__init__(ops)
+        self.hidden_size, self.heads, self.qk_heads = int(hidden_size), int(n_heads), int(n_qk_heads)
+        self.d, self.dv, self.taps, self.eps = int(head_dim), int(value_dim), int(conv_taps), float(eps)
+        if self.heads % self.qk_heads:
+            raise ValueError(f"{self.heads} value heads cannot be grouped over {self.qk_heads} query/key heads")
+        if not 1 <= self.taps <= 8:
+            raise ValueError(f"gated_delta_rule: the convolution kernel takes 1 to 8 taps, got {self.taps}")
+        self.names = dict(self.DEFAULT_NAMES, **(dict(names) if names else {}))
+        self.channels = 2 * self.qk_heads * self.d + self.heads * self.dv
+
+    def weight_specs(self) -> Dict[str, WeightSpec]:
+        n, W, H, G, d, dv, K = self.names, self.hidden_size, self.heads, self.qk_heads, self.d, self.dv, self.taps
+        return {n["q"]: WeightSpec((G * d, W)), n["q"] + n["conv"]: WeightSpec((G * d, K), "vector"),
+                n["k"]: WeightSpec((G * d, W)), n["k"] + n["conv"]: WeightSpec((G * d, K), "vector"),
+                n["v"]: WeightSpec((H * dv, W)), n["v"] + n["conv"]: WeightSpec((H * dv, K), "vector"),
+                n["b"]: WeightSpec((H, W)), n["a"]: WeightSpec((H, W)), n["A_log"]: WeightSpec((H,), "vector"),
+                n["dt_bias"]: WeightSpec((H,), "vector"), n["g"]: WeightSpec((H * dv, W)), n["o"]: WeightSpec((W, H * dv)),
+                n["norm"]: WeightSpec((dv,), "vector")}
+
+    def load_weights(self, tensors: Dict[str, torch.Tensor]) -> None:
+        n = self.names
+        self.w_in = self.ops.keep(torch.cat([tensors[n[x]] for x in ("q", "k", "v", "g", "b", "a")], dim=0).contiguous())
+        self.w_o = self.ops.keep(tensors[n["o"]].contiguous())
+        self.w_taps = self._keep32(torch.cat([tensors[n[x] + n["conv"]].float() for x in ("q", "k", "v")], dim=0))
+        self.a_log = self._keep32(tensors[n["A_log"]])
+        self.dt_bias = self._keep32(tensors[n["dt_bias"]])
+        self.w_norm = self._keep32(tensors[n["norm"]])
+
+    def weight_bytes(self) -> int:
+        return sum(t.numel() * t.element_size() for t in (self.w_in, self.w_o, self.w_taps, self.a_log, self.dt_bias, self.w_norm))
+
+    def cache_needs(self) -> CacheNeeds:
+        return CacheNeeds(state={"matrix_state": ((self.heads, self.d, self.dv), torch.float32),
+                                 "conv_inputs": ((max(self.taps - 1, 1), self.channels), torch.float32)})
+
+    def cache_bytes_read(self, kv_len: int) -> int:
+        return super().cache_bytes_read(kv_len) + 4 * max(self.taps - 1, 1) * self.channels
+
+    def forward(self, ctx, y: torch.Tensor, lane, writes_cache: bool) -> torch.Tensor:
+        ops, H, G, d, dv = self.ops, self.heads, self.qk_heads, self.d, self.dv
+        C = self.channels
+        proj = ops.linear(y, self.w_in, out_f32=True)                       # [q | k | v | g | b | a]
+        b_col = C + H * dv
+        q, k, v, beta, decay = ops.conv_prepare(ctx, proj, self.w_taps, lane.state["conv_inputs"], self.a_log, self.dt_bias,
+                                                b_col, b_col + H, H, G, d, dv, self.UNIT_EPS)
+        o = ops.linear_recurrence(ctx, q, k, v, decay, beta, lane.state["matrix_state"], H, G, d, dv, d ** -0.5)
+        return ops.linear(ops.gated_head_norm(o, proj[:, C:C + H * dv], self.w_norm, self.eps), self.w_o)

@@ -87,3 +87,37 @@ class LayerNorm(Norm):
         """x += norm(a) in place; with ``then``, also returns then(x)."""
         return self.ops.post_norm_add(x, a, self.weight, self.bias, self.eps,
                                       None if then is None else (then.weight, then.bias))
+
+
+@NORMS.register("scalar_rms_norm")
+class ScalarRMSNorm(Norm):
+    """RMS norm with one number for all coordinates: y = x / sqrt(mean(x^2) + eps) * g.  The tensor ``weight_name``
+    below the part's prefix holds g (no axes).  The plain forms run on the RMS-norm kernel with g spread over the
+    width; ``gain`` (one 32-bit float on the device) is what a kernel that norms as part of a larger pass takes."""
+
+    recordable_prompt = True
+
+    def __init__(self, ops, hidden_size: int, eps: float, weight_name: str = "weight"):
+        super().__init__(ops)
+        self.hidden_size, self.eps = int(hidden_size), float(eps)
+        self.weight_name = str(weight_name)
+        self.gain: Optional[torch.Tensor] = None
+        self.weight: Optional[torch.Tensor] = None
+
+    def weight_specs(self) -> Dict[str, WeightSpec]:
+        return {self.weight_name: WeightSpec((), "vector")}
+
+    def load_weights(self, tensors: Dict[str, torch.Tensor]) -> None:
+        g = tensors[self.weight_name].float().reshape(1)
+        self.gain = self.ops.keep(g.contiguous())
+        self.weight = self.ops.keep(g.expand(self.hidden_size).contiguous())
+
+    def weight_bytes(self) -> int:
+        return 4
+
+    def forward(self, x: torch.Tensor, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+        return self.ops.add_rmsnorm(x, None, 0.0, self.weight, self.eps, rows)
+
+    def add_forward(self, x: torch.Tensor, delta: torch.Tensor, scale: float,
+                    rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+        return self.ops.add_rmsnorm(x, delta, scale, self.weight, self.eps, rows)

@@ -20,6 +20,9 @@ class Architecture:
     model_spec: Callable[[Any], ModelSpec]              # typed config -> specification
     adapt_tensor: Optional[Callable[[Any, str, Any], List[Tuple[str, Any]]]] = None
     ignore_tensor: Optional[Callable[[str], bool]] = None
+    # (typed config, {tensor name: shape}) -> typed config: fills in sizes that the configuration leaves to the
+    # checkpoint's tensors; called by ``load_config`` when the folder holds a checkpoint
+    fit_config: Optional[Callable[[Any, Dict[str, Tuple[int, ...]]], Any]] = None
 
 
 _ARCHITECTURES: Dict[str, Architecture] = {}
@@ -73,7 +76,21 @@ def load_config(model_dir: str):
     """(architecture, typed configuration) of a model folder."""
     data = read_config_json(model_dir)
     arch = architecture(architecture_name(data))
-    return arch, arch.config_class.from_dict(data)
+    config = arch.config_class.from_dict(data)
+    if arch.fit_config is not None:
+        import os
+        from .weights.safetensors_io import SafetensorsError, SafetensorsFile, model_files
+        shapes: Dict[str, Tuple[int, ...]] = {}
+        try:
+            for path in (model_files(model_dir) if os.path.isdir(model_dir) else []):
+                f = SafetensorsFile(path)
+                shapes.update({name: entry[1] for name, entry in f.entries.items()})
+                f.close()
+        except (SafetensorsError, OSError):
+            shapes = {}                      # the loader reports a broken checkpoint in its own words
+        if shapes:
+            config = arch.fit_config(config, shapes)
+    return arch, config
 
 
 def _register_builtin() -> None:
@@ -91,6 +108,11 @@ def _register_builtin() -> None:
     from .models import reravik
 
     register_architecture(Architecture(name=ReravikConfig.architecture, config_class=ReravikConfig, model_spec=reravik.model_spec))
+    from .config.mufevik import MufevikConfig
+    from .models import mufevik
+
+    register_architecture(Architecture(name=MufevikConfig.architecture, config_class=MufevikConfig, model_spec=mufevik.model_spec,
+                                       fit_config=mufevik.fit_config_to_checkpoint))
 
 
 _register_builtin()
