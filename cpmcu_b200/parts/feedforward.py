@@ -141,6 +141,9 @@ class RoutedExperts(FeedForward):
         logits = ops.linear(y, self.w_router, out_f32=True)
         chosen, weights, gate = ops.moe_route(logits, self.correction, self.E, self.top, self.n_groups, self.keep,
                                               gate_col=self.E if self.shared is not None else -1)
+        taps = ctx.extras.get("taps")
+        if taps is not None and not ctx.captured and taps.get("experts") is not None:
+            taps["experts"].append(chosen.clone())          # a caller that wants to see the choice (tests do)
         pairs = ops.moe_experts(y, chosen, self.w_gate, self.w_up, self.w_down)
         shared = self.shared.forward(ctx, y) if self.shared is not None else None
         return ops.moe_combine(pairs, weights, shared, gate)

@@ -64,6 +64,21 @@ def talking_softmax_attention(h: torch.Tensor, w: Dict[str, torch.Tensor], p: st
     return out.reshape(T, H * dv) @ w[p + "o"].T
 
 
+def matrix_recurrence(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay: torch.Tensor,
+                      beta: Optional[torch.Tensor] = None, state: Optional[torch.Tensor] = None):
+    """q, k [T, H, d], v [T, H, dv], decay [T, H, d] or [T, H, 1], beta [T, H] or None (no delta correction).
+    S <- diag(decay) S; u = v or beta (v - S^T k); S <- S + k u^T; o = S^T q.  Returns (o [T, H, dv], last S)."""
+    T, H, d = q.shape
+    S = torch.zeros(H, d, v.shape[-1], dtype=q.dtype) if state is None else state.clone()
+    out = torch.empty(T, H, v.shape[-1], dtype=q.dtype)
+    for t in range(T):
+        S = decay[t][:, :, None] * S
+        u = v[t] if beta is None else beta[t][:, None] * (v[t] - torch.einsum("hcv,hc->hv", S, k[t]))
+        S = S + k[t][:, :, None] * u[:, None, :]
+        out[t] = torch.einsum("hcv,hc->hv", S, q[t])
+    return out, S
+
+
 def gated_linear_attention(h: torch.Tensor, w: Dict[str, torch.Tensor], p: str, m: dict, eps: float) -> torch.Tensor:
     """Per head S_t = diag(alpha_t) S_(t-1) + k_t v_t^T, o_t = S_t^T q_t, alpha = sigmoid(z)^(1/tau) per key channel."""
     T = h.shape[0]
@@ -73,11 +88,7 @@ def gated_linear_attention(h: torch.Tensor, w: Dict[str, torch.Tensor], p: str, 
     v = (h @ w[p + "v"].T).view(T, H, dv)
     z = (h @ w[p + "a1"].T) @ w[p + "a2"].T + w[p + "a2.b"]
     alpha = torch.pow(torch.sigmoid(z), 1.0 / m["tau"]).view(T, H, d)
-    S = torch.zeros(H, d, dv, dtype=h.dtype)
-    out = torch.empty(T, H, dv, dtype=h.dtype)
-    for t in range(T):
-        S = alpha[t][:, :, None] * S + k[t][:, :, None] * v[t][:, None, :]
-        out[t] = torch.einsum("hcv,hc->hv", S, q[t])
+    out, _ = matrix_recurrence(q, k, v, alpha)
     out = rms_norm(out, w[p + "norm"], eps).reshape(T, H * dv)
     return (out * silu(h @ w[p + "g"].T)) @ w[p + "o"].T
 
@@ -110,15 +121,7 @@ def gated_delta_rule(h: torch.Tensor, w: Dict[str, torch.Tensor], p: str, m: dic
     beta = torch.sigmoid(h @ w[p + "b"].T)                                                   # [T, H]
     decay = torch.exp(-torch.exp(w[p + "A_log"]) * torch.nn.functional.softplus(h @ w[p + "a"].T + w[p + "dt_bias"]))
     rep = H // G
-    S = torch.zeros(H, d, dv, dtype=h.dtype)
-    out = torch.empty(T, H, dv, dtype=h.dtype)
-    for t in range(T):
-        kt = k[t].repeat_interleave(rep, dim=0)                                              # [H, d]
-        qt = q[t].repeat_interleave(rep, dim=0)
-        S = decay[t][:, None, None] * S
-        u = beta[t][:, None] * (v[t] - torch.einsum("hcv,hc->hv", S, kt))
-        S = S + kt[:, :, None] * u[:, None, :]
-        out[t] = torch.einsum("hcv,hc->hv", S, qt)
+    out, _ = matrix_recurrence(q.repeat_interleave(rep, dim=1), k.repeat_interleave(rep, dim=1), v, decay[:, :, None], beta)
     out = rms_norm(out, w[p + "norm"], eps).reshape(T, H * dv)
     return (out * silu(h @ w[p + "g"].T)) @ w[p + "o"].T
 
@@ -127,25 +130,65 @@ def gated_expert(h: torch.Tensor, w: Dict[str, torch.Tensor], p: str) -> torch.T
     return (silu(h @ w[p + "gate"].T) * (h @ w[p + "up"].T)) @ w[p + "down"].T
 
 
-def route(h: torch.Tensor, w: Dict[str, torch.Tensor], p: str, r: dict):
-    """(chosen experts [T, top], their weights [T, top]): softmax scores, choice by score + correction among the
-    experts of the best groups, weights the plain scores of the chosen."""
-    E, top = r["experts"], r["top"]
+def route_scores(z: torch.Tensor, correction: torch.Tensor, r: dict):
+    """Router logits z [T, E] -> (scores s, choice scores with the experts of groups that are not kept at -inf)."""
+    E = r["experts"]
     groups = r.get("groups") or {"count": 1, "keep": 1}
-    s = torch.softmax(h @ w[p + "router"].T, dim=-1)
-    choice = s + w[p + "correction"]
+    s = torch.softmax(z, dim=-1)
+    choice = s + correction
     per = E // groups["count"]
     best = choice.view(-1, groups["count"], per).max(-1).values
     kept = best.topk(groups["keep"], dim=-1).indices
-    allowed = torch.zeros(h.shape[0], groups["count"], dtype=torch.bool)
+    allowed = torch.zeros(z.shape[0], groups["count"], dtype=torch.bool)
     allowed.scatter_(1, kept, True)
-    choice = choice.masked_fill(~allowed.repeat_interleave(per, dim=1), float("-inf"))
-    chosen = choice.topk(top, dim=-1).indices
+    return s, choice.masked_fill(~allowed.repeat_interleave(per, dim=1), float("-inf"))
+
+
+def route(h: torch.Tensor, w: Dict[str, torch.Tensor], p: str, r: dict):
+    """(chosen experts [T, top], their weights [T, top]): softmax scores, choice by score + correction among the
+    experts of the best groups, weights the plain scores of the chosen."""
+    s, choice = route_scores(h @ w[p + "router"].T, w[p + "correction"], r)
+    chosen = choice.topk(r["top"], dim=-1).indices
     return chosen, torch.gather(s, 1, chosen)
 
 
-def mixture_of_experts(h: torch.Tensor, w: Dict[str, torch.Tensor], p: str, mlp: dict) -> torch.Tensor:
+def choice_slack(raw: torch.Tensor, forced: torch.Tensor, r: dict) -> List[float]:
+    """How far a given choice of experts lies from the rule's, per token: the larger of (the lowest kept group's score
+    minus the lowest score of a group the choice uses) and (the rule's cut-off among the experts of the groups the
+    choice uses, completed by the best others, minus the lowest chosen choice score); 0 when the choice is the rule's."""
+    groups = r.get("groups") or {"count": 1, "keep": 1}
+    count, keep, top = groups["count"], groups["keep"], r["top"]
+    per = r["experts"] // count
+    out = []
+    for t in range(raw.shape[0]):
+        gbest = raw[t].view(count, per).max(-1).values
+        order = gbest.argsort(descending=True).tolist()
+        used = sorted(set((forced[t] // per).tolist()))
+        g_slack = max(0.0, float(gbest[order[keep - 1]] - min(gbest[g] for g in used)))
+        for g in order:
+            if len(used) >= keep:
+                break
+            if g not in used:
+                used.append(g)
+        mask = torch.full_like(raw[t], float("-inf"))
+        for g in used:
+            mask[g * per:(g + 1) * per] = 0.0
+        cut = (raw[t] + mask).topk(top).values.min()
+        out.append(max(g_slack, float(cut - raw[t][forced[t]].min()), 0.0) if len(used) <= keep else float("inf"))
+    return out
+
+
+def mixture_of_experts(h: torch.Tensor, w: Dict[str, torch.Tensor], p: str, mlp: dict,
+                       forced: Optional[torch.Tensor] = None, slack: Optional[List[float]] = None) -> torch.Tensor:
+    """``forced`` [T, top]: experts to use instead of the rule's own choice (the weights stay the scores s); ``slack``
+    then receives, per token, how far the lowest forced choice score lies below the rule's cut-off (0: the rule's choice)."""
     chosen, weight = route(h, w, p, mlp["router"])
+    if forced is not None:
+        forced = forced.long()
+        s, _ = route_scores(h @ w[p + "router"].T, w[p + "correction"], mlp["router"])
+        if slack is not None:
+            slack.extend(choice_slack(s + w[p + "correction"], forced, mlp["router"]))
+        chosen, weight = forced, torch.gather(s, 1, forced)
     out = torch.zeros(h.shape[0], w[p + "e0.down"].shape[0], dtype=h.dtype)
     for t in range(h.shape[0]):
         for e, g in zip(chosen[t].tolist(), weight[t]):
@@ -173,9 +216,11 @@ def mixer(h, w, p, layer, eps):
     raise ValueError(layer["type"])
 
 
-def forward(config: dict, weights: Dict[str, torch.Tensor], ids: Sequence[int], collect: Optional[List[torch.Tensor]] = None) -> torch.Tensor:
+def forward(config: dict, weights: Dict[str, torch.Tensor], ids: Sequence[int], collect: Optional[List[torch.Tensor]] = None,
+            forced: Optional[List[torch.Tensor]] = None, slack: Optional[List[float]] = None) -> torch.Tensor:
     """Logits [T, vocab] of one whole sequence.  ``collect`` receives the residual stream (the sum of the streams)
-    after every layer."""
+    after every layer.  ``forced``: per layer with a mixture of experts (in order), the experts [T, top] to use."""
+    forced = list(forced) if forced is not None else None
     w = {k: (v.to(DT) if v.is_floating_point() else v) for k, v in weights.items()}
     eps = config["norm"]["eps"]
     hyper = "streams" in config
@@ -186,7 +231,8 @@ def forward(config: dict, weights: Dict[str, torch.Tensor], ids: Sequence[int], 
         L = f"l{i}."
         subs = [("1", lambda hh: mixer(hh, w, L + "mix.", layer, eps))]
         if layer.get("mlp"):
-            subs.append(("2", lambda hh: mixture_of_experts(hh, w, L + "mlp.", layer["mlp"])))
+            f = forced.pop(0) if forced else None
+            subs.append(("2", lambda hh, f=f: mixture_of_experts(hh, w, L + "mlp.", layer["mlp"], f, slack)))
         for n, fn in subs:
             if hyper:
                 u = hyper_read(x, w, f"{L}hc{n}.")
@@ -197,3 +243,15 @@ def forward(config: dict, weights: Dict[str, torch.Tensor], ids: Sequence[int], 
             collect.append(x.sum(1))
     y = scalar_rms_norm(x.sum(1), w["final.norm"], eps)
     return (y @ w["head"].T) * config.get("logit_scale", 1.0)
+
+
+def greedy(config: dict, weights: Dict[str, torch.Tensor], prompt: Sequence[int], n_new: int):
+    """(tokens, gaps): the ``n_new`` tokens greedy decoding appends, and at each the gap between the two best logits."""
+    ids, tokens, gaps = list(prompt), [], []
+    for _ in range(n_new):
+        last = forward(config, weights, ids)[-1]
+        best = torch.topk(last, 2)
+        tokens.append(int(best.indices[0]))
+        gaps.append(float(best.values[0] - best.values[1]))
+        ids.append(tokens[-1])
+    return tokens, gaps

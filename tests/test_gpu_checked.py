@@ -27,7 +27,7 @@ with tempfile.TemporaryDirectory() as tmp:
         assert all(len(r.tokens) == 8 for r in res)
         llm.ops.raise_on_kernel_error()                 # bounds records of every file, guard words of every region
         assert llm.storage.arena.guards and len(llm.storage.arena.guard_at) == 6
-assert "checked" in library.library_path() and len(library.load().checked_files) == 6
+assert "checked" in library.library_path() and len(library.load().checked_files) == len(library.BOUNDS_FILES)
 print("CLEAN OK")
 '''
 
