@@ -738,6 +738,264 @@ def workload_reravik(steps: int, warmup: int, size: str, batch: int) -> int:
     return 0
 
 
+# Mufevik at sizes that resemble a real model's layers: eight layers (gated delta rule, two layers of attention beside
+# gated linear attention, delta rule, ...), four residual streams, routed experts; random weights N(0, 0.02), vectors
+# 1 + N(0, 0.02), stream mixes the identity.
+MUFEVIK_SIZES = {
+    "1k": dict(width=1024, heads=16, kv_heads=4, dim=64, vdim=64, lin_heads=8, lin_dim=64, lin_vdim=128, delta_heads=16,
+               delta_qk_heads=8, delta_dim=64, delta_vdim=64, conv=4, experts=32, top=4, groups=4, keep=2, ff=512, shared=1024,
+               streams=4, vocab=32000),
+    "2k": dict(width=2048, heads=16, kv_heads=4, dim=128, vdim=128, lin_heads=16, lin_dim=64, lin_vdim=128, delta_heads=16,
+               delta_qk_heads=8, delta_dim=128, delta_vdim=128, conv=4, experts=64, top=6, groups=8, keep=4, ff=768, shared=1536,
+               streams=4, vocab=32000),
+}
+
+
+def mufevik_config(z: dict) -> dict:
+    mlp = {"kind": "moe", "router": {"experts": z["experts"], "top": z["top"], "groups": {"count": z["groups"], "keep": z["keep"]}},
+           "expert": {"ff": z["ff"]}, "shared": {"ff": z["shared"]}}
+    par = {"type": "parallel", "mlp": mlp,
+           "mixer": {"left": {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["vdim"],
+                              "scale": z["dim"] ** -0.5, "rot": {"dims": z["dim"], "base": 10000.0}},
+                     "right": {"heads": z["lin_heads"], "dim": z["lin_dim"], "vdim": z["lin_vdim"], "tau": 16.0, "rank": 16}}}
+    delta = {"type": "delta", "mlp": mlp, "mixer": {"heads": z["delta_heads"], "kv_heads": z["delta_qk_heads"], "dim": z["delta_dim"],
+                                                     "vdim": z["delta_vdim"], "conv": z["conv"]}}
+    return {"architecture": "Mufevik", "vocab": z["vocab"], "width": z["width"], "streams": z["streams"], "logit_scale": 1.0,
+            "norm": {"eps": 1e-5}, "layers": [delta, par, par, delta, delta, par, par, delta]}
+
+
+def build_mufevik(z: dict, max_tokens: int, max_batch: int, context: int):
+    import torch
+    from cpmcu_b200.engine import Stepper
+    from cpmcu_b200.engine.storage import make_storage
+    from cpmcu_b200.loading import build_model
+    from cpmcu_b200.registry import architecture
+    from cpmcu_b200.weights import random_tensors
+
+    arch = architecture("Mufevik")
+    cfg = arch.config_class.from_dict(mufevik_config(z))
+    model = build_model(arch, cfg, torch.bfloat16, "cuda:0")
+    storage = make_storage(model, PREFILL_TOKENS, max_batch, max_tokens=max_tokens, max_seq_tokens=context + 64, n_slots=max_batch + 2)
+    tensors = random_tensors(model.weight_specs(), 5, torch.bfloat16, std=0.02, norm_mean=1.0, device="cuda:0")
+    S = z["streams"]
+    for name, t in tensors.items():
+        if ".hc" in name and name.endswith(".mix"):
+            t.copy_(torch.eye(S, dtype=t.dtype, device=t.device))
+        elif ".hc" in name and name.endswith(".in"):
+            t.fill_(1.0 / S)
+        elif name.endswith(".talk"):
+            t.copy_(torch.eye(t.shape[0], dtype=t.dtype, device=t.device))
+        elif name.endswith((".conv", ".correction", ".A_log", ".dt_bias")):
+            t.mul_(0.3)
+    model.load_weights(tensors)
+    del tensors
+    torch.cuda.empty_cache()
+    return cfg, model, storage.cache, Stepper(model, storage.cache, chunk_tokens=PREFILL_TOKENS, graph_prompts=True)
+
+
+def mufevik_kernels(z: dict, pk: dict, context: int, batch: int) -> dict:
+    """Every kernel of the design alone, at the size's shapes, beside the like kernel of the closest models (the dense
+    model's attention, norm, rotary store and gated product; the other recurrent design's scan): a prompt of 2,048
+    tokens and a decode step of ``batch`` sequences at ``context`` tokens.  CUDA events around one launch after a
+    flush of L2 (a 512 MB buffer is written), median of five; bytes and FLOPs are the algorithmic ones."""
+    import torch
+    from cpmcu_b200.cache import Cache
+    from cpmcu_b200.ops.ops import Ops
+    from cpmcu_b200.parts.base import CacheNeeds, QUERY_TILE_TOKENS, StepContext
+
+    ops = Ops(torch.bfloat16)
+    dev = "cuda:0"
+    flush = torch.empty(512 << 20, dtype=torch.uint8, device=dev)
+    W, H, G, d, dv, S = z["width"], z["heads"], z["kv_heads"], z["dim"], z["vdim"], z["streams"]
+    T = PREFILL_TOKENS
+    i32 = dict(dtype=torch.int32, device=dev)
+
+    def timed(fn):
+        ts = []
+        for _ in range(6):
+            flush.fill_(1)
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            ts.append(e0.elapsed_time(e1))
+        return statistics.median(ts[1:])
+
+    def context_of(q_lens, starts, slots):
+        pos = torch.cat([torch.arange(s, s + n) for n, s in zip(q_lens, starts)]).to(**i32)
+        seq = torch.cat([torch.full((n,), i) for i, n in enumerate(q_lens)]).to(**i32)
+        cu = torch.tensor([0] + [sum(q_lens[:i + 1]) for i in range(len(q_lens))], **i32)
+        kv = [s + n for n, s in zip(q_lens, starts)]
+        ctx = StepContext(n_tokens=sum(q_lens), n_seqs=len(q_lens), is_decode=all(n == 1 for n in q_lens), captured=False,
+                          q_lens=list(q_lens), kv_lens=kv, slots=list(slots), max_q_len=max(q_lens), max_kv_len=max(kv),
+                          token_ids=torch.zeros(sum(q_lens), **i32), positions=pos, token_seq=seq, cu_q=cu,
+                          kv_len_dev=torch.tensor(kv, **i32), slot_dev=torch.tensor(list(slots), **i32))
+        ts = [i for i, n in enumerate(q_lens) for _ in range(0, n, QUERY_TILE_TOKENS)]
+        tr = [r for n in q_lens for r in range(0, n, QUERY_TILE_TOKENS)]
+        ctx.q_tiles = (torch.tensor(ts, **i32), torch.tensor(tr, **i32), len(ts))
+        return ctx
+
+    out = {}
+
+    def note(name, ms, nbytes=0.0, flops=0.0, like=None):
+        row = {"us": ms * 1e3}
+        if nbytes:
+            row["gbs"] = nbytes / (ms * 1e-3) / 1e9
+            row["frac_hbm"] = row["gbs"] / pk["hbm_gbs"]
+        if flops:
+            row["tflops"] = flops / (ms * 1e-3) / 1e12
+            row["frac_bf16"] = row["tflops"] / pk["bf16_tflops"]
+        if like:
+            row["like"] = like
+        out[name] = row
+
+    n_slots = batch + 2
+    own = Cache([CacheNeeds(kv_heads=G, head_dim=d, value_dim=dv if dv != d else 0)], max_tokens=(batch + 1) * (context + 64),
+                dtype=torch.bfloat16, device=dev, n_slots=n_slots)
+    dense = Cache([CacheNeeds(kv_heads=2, head_dim=d)], max_tokens=(batch + 1) * (context + 64), dtype=torch.bfloat16, device=dev,
+                  n_slots=n_slots)
+    slots = []
+    for c in (own, dense):
+        slots = [c.open_sequence() for _ in range(batch)]
+        for s_ in slots:
+            c.reserve(s_, context)
+        c.sync()
+        c.lane(0).k.normal_(0, 0.5)
+        c.lane(0).v.normal_(0, 0.5)
+    E, top, ff = z["experts"], z["top"], z["ff"]
+    DH, DG, dd, ddv, K = z["delta_heads"], z["delta_qk_heads"], z["delta_dim"], z["delta_vdim"], z["conv"]
+    LH, ld, ldv = z["lin_heads"], z["lin_dim"], z["lin_vdim"]
+    wg = torch.randn(E, ff, W, device=dev).bfloat16() * 0.02
+    wu = torch.randn(E, ff, W, device=dev).bfloat16() * 0.02
+    wd = torch.randn(E, W, ff, device=dev).bfloat16() * 0.02
+    for phase, q_lens, starts in (("prefill", [T], [0]), ("decode", [1] * batch, [context - 1] * batch)):
+        ctx = context_of(q_lens, starts, slots[:len(q_lens)])
+        n = ctx.n_tokens
+        keys = [s + j + 1 for nq, s in zip(q_lens, starts) for j in range(nq)]
+        X = torch.randn(n, S, W, device=dev)
+        y = torch.randn(n, W, device=dev).bfloat16()
+        mix, vec, gain = torch.eye(S, device=dev), torch.ones(S, device=dev), torch.ones(1, device=dev)
+        note(f"{phase}/hyper_step (write + read + norm)", timed(lambda: ops.hyper_step(X, (y, mix, vec), (vec, gain), 1e-5)),
+             n * W * (8.0 * S + 4.0), like="add_rmsnorm")
+        x1 = torch.randn(n, W, device=dev)
+        wn = torch.ones(W, device=dev)
+        note(f"{phase}/add_rmsnorm (dense model)", timed(lambda: ops.add_rmsnorm(x1, y, 1.0, wn, 1e-5)), n * W * 12.0)
+        # attention whose weights are mixed across heads, beside the dense model's
+        qkv = torch.randn(n, (H + G) * d + G * dv, device=dev).bfloat16()
+        inv = torch.ones(d // 2, device=dev)
+        ol = own.lane(0)
+        note(f"{phase}/rope_store_dv", timed(lambda: ops.rope_store_dv(ctx, qkv, ol, H, G, d, dv, inv, d)),
+             n * ((H + G) * d + G * dv) * 2.0 * 2, like="rope_store")
+        q = torch.randn(n, H, d, device=dev).bfloat16()
+        temp, talk = torch.ones(H, device=dev), torch.eye(H, device=dev)
+        note(f"{phase}/talking_attention", timed(lambda: ops.talking_attention(ctx, q, ol, G, dv, d ** -0.5, temp, talk)),
+             nbytes=(sum(s + nq for nq, s in zip(q_lens, starts)) * G * (d + dv) * 2.0) if phase == "decode" else 0.0,
+             flops=2.0 * H * (d + dv) * sum(keys), like="attention")
+        dl = dense.lane(0)
+        qkv2 = torch.randn(n, (H + 4) * d, device=dev).bfloat16()
+        note(f"{phase}/rope_store (dense model)",
+             timed(lambda: ops.rope_store(qkv2, H, 2, d, ctx.positions, ctx.token_seq, ctx.slot_dev, dl.page_table, dl.k, dl.v, inv, 1.0, d)),
+             n * (H + 4) * d * 2.0 * 2)
+        note(f"{phase}/attention (dense model, 2 kv heads)", timed(lambda: ops.attention(ctx, q, dl, 2, d ** -0.5)),
+             nbytes=(sum(s + nq for nq, s in zip(q_lens, starts)) * 2 * 2 * d * 2.0) if phase == "decode" else 0.0,
+             flops=4.0 * H * d * sum(keys))
+        # the two recurrences, beside the other recurrent design's scan
+        C = 2 * DG * dd + DH * ddv
+        proj = torch.randn(n, C + DH * ddv + 2 * DH, device=dev)
+        taps = torch.randn(C, K, device=dev) * 0.3
+        cstate = torch.zeros(n_slots, K - 1, C, device=dev)
+        al, db = torch.zeros(DH, device=dev), torch.zeros(DH, device=dev)
+        note(f"{phase}/conv_prepare", timed(lambda: ops.conv_prepare(ctx, proj, taps, cstate, al, db, C + DH * ddv, C + DH * ddv + DH, DH, DG, dd, ddv, 1e-6)),
+             n * C * 8.0, like="rope_store")
+        qd, kd, vd_, beta, decay = ops.conv_prepare(ctx, proj, taps, cstate, al, db, C + DH * ddv, C + DH * ddv + DH, DH, DG, dd, ddv, 1e-6)
+        dstate = torch.zeros(n_slots, DH, dd, ddv, device=dev)
+        state_bytes = len(q_lens) * DH * dd * ddv * 8.0
+        note(f"{phase}/linear_recurrence (delta rule)",
+             timed(lambda: ops.linear_recurrence(ctx, qd, kd, vd_, decay, beta, dstate, DH, DG, dd, ddv, dd ** -0.5)),
+             nbytes=state_bytes + n * (2 * DG * dd + 2 * DH * ddv) * 4.0, flops=6.0 * n * DH * dd * ddv, like="mingru_scan")
+        ql, kl, vl = torch.randn(n, LH * ld, device=dev), torch.randn(n, LH * ld, device=dev), torch.randn(n, LH * ldv, device=dev)
+        al2 = torch.rand(n, LH * ld, device=dev) * 0.1 + 0.9
+        lstate = torch.zeros(n_slots, LH, ld, ldv, device=dev)
+        note(f"{phase}/linear_recurrence (decay per channel)",
+             timed(lambda: ops.linear_recurrence(ctx, ql, kl, vl, al2, None, lstate, LH, LH, ld, ldv, ld ** -0.5, vector_decay=True)),
+             nbytes=len(q_lens) * LH * ld * ldv * 8.0 + n * (3 * LH * ld + 2 * LH * ldv) * 4.0, flops=4.0 * n * LH * ld * ldv,
+             like="mingru_scan")
+        gp = torch.randn(n, 3 * W, device=dev)
+        gstate = torch.zeros(n_slots, W, device=dev)
+        note(f"{phase}/mingru_scan (other recurrent design)", timed(lambda: ops.mingru_scan(ctx, gp, wn, wn, gstate, W)), n * W * 14.0)
+        o = torch.randn(n, DH, ddv, device=dev)
+        wv = torch.ones(ddv, device=dev)
+        note(f"{phase}/gated_head_norm", timed(lambda: ops.gated_head_norm(o, proj[:, C:C + DH * ddv], wv, 1e-5)), n * DH * ddv * 10.0,
+             like="add_rmsnorm")
+        a2, b2 = torch.randn(n, W, device=dev).bfloat16(), torch.randn(n, W, device=dev).bfloat16()
+        note(f"{phase}/dual_rmsnorm_mean", timed(lambda: ops.dual_rmsnorm_mean(a2, b2, wn, wn, 1e-5)), n * W * 6.0, like="add_rmsnorm")
+        # routed experts, beside the dense model's gated product of the same active size
+        logits = torch.randn(n, E + 1, device=dev)
+        corr = torch.zeros(E, device=dev)
+        note(f"{phase}/moe_route", timed(lambda: ops.moe_route(logits, corr, E, top, z["groups"], z["keep"], E)), n * (E + 1) * 4.0)
+        chosen, weights, gate = ops.moe_route(logits, corr, E, top, z["groups"], z["keep"], E)
+        yy = torch.randn(n, W, device=dev).bfloat16()
+        used = int(torch.unique(chosen).numel())
+        note(f"{phase}/moe_experts (group + gate/up + down)", timed(lambda: ops.moe_experts(yy, chosen, wg, wu, wd)),
+             nbytes=used * 3.0 * ff * W * 2.0 + n * top * (W + ff) * 4.0, flops=6.0 * n * top * ff * W, like="gate_up product + down")
+        act = top * ff
+        gu_w = torch.randn(2 * act, W, device=dev).bfloat16() * 0.02
+        dn_w = torch.randn(W, act, device=dev).bfloat16() * 0.02
+        note(f"{phase}/gate_up product + down of {act} (dense model)", timed(lambda: ops.linear(ops.gated_linear(yy, gu_w, 8, 0), dn_w)),
+             nbytes=3.0 * act * W * 2.0 + n * (2 * W + act) * 2.0, flops=6.0 * n * act * W)
+        pairs = ops.moe_experts(yy, chosen, wg, wu, wd)
+        note(f"{phase}/moe_combine", timed(lambda: ops.moe_combine(pairs, weights, yy, gate)), n * W * 2.0 * (top + 2), like="add_rmsnorm")
+    return out
+
+
+def workload_mufevik(steps: int, warmup: int, size: str, batch: int) -> int:
+    """Mufevik at one of MUFEVIK_SIZES beside MiniCPM4 with equal hidden size and heads, a feed-forward as large as a
+    token's active experts (``top`` routed and the shared one) and as many layers: decode steps of ``batch`` sequences
+    ending at a context of 4,096 tokens under a CUDA graph, a prompt of 2,048 tokens, and every kernel of the design
+    alone beside its like."""
+    import torch
+
+    z, pk, context = MUFEVIK_SIZES[size], peaks(), CONTEXT
+    cfg, model, cache, stepper = build_mufevik(z, batch * (context + 64) + 128, batch, context)
+    runs = len(model.schedule)
+    pre_ms = time_prefill_any(stepper, cfg.vocab)
+    ms, clocks, launches, cache_bytes = time_decode(stepper, batch, steps, warmup, cfg.vocab, True, context=context)
+    weight_bytes = model.weight_bytes_per_step()
+    achieved = (weight_bytes + cache_bytes) / (ms * 1e-3) / 1e9
+    del model, cache, stepper
+    torch.cuda.empty_cache()
+    active = z["top"] * z["ff"] + z["shared"]
+    like = dict(MODEL, hidden_size=z["width"], intermediate_size=active, num_attention_heads=z["heads"], num_key_value_heads=2,
+                head_dim=z["dim"], vocab_size=z["vocab"])
+    dcfg, dmodel, dcache, dstepper = build_engine(runs, batch * (context + 64) + 128, batch, model=like, max_seq_tokens=context + 64)
+    d_pre = time_prefill_any(dstepper, dcfg.vocab_size)
+    d_ms, _, d_launches, d_cache = time_decode(dstepper, batch, steps, warmup, dcfg.vocab_size, False, context=context)
+    d_weights = dmodel.weight_bytes_per_step()
+    d_achieved = (d_weights + d_cache) / (d_ms * 1e-3) / 1e9
+    del dmodel, dcache, dstepper
+    torch.cuda.empty_cache()
+    kernels = mufevik_kernels(z, pk, context, batch)
+    print(json.dumps({
+        "workload": "mufevik", "metric": f"decode tokens/s (Mufevik {size} sizes, bf16, batch {batch}, context {context})",
+        "value": batch * 1000.0 / ms, "unit": "tokens/s", "ms_per_step": ms, "steps": steps, "warmup": warmup, "dtype": "bf16",
+        "data": "synthetic: uniform-random token ids, random weights N(0,0.02) seed 5",
+        "config": dict(z, size=size, layers=len(cfg.layers), global_batch=batch, seq_len=context, prefill_tokens=PREFILL_TOKENS,
+                       cuda_graph=True, peaks=pk["source"]),
+        "prefill": {"value": PREFILL_TOKENS / (pre_ms * 1e-3), "ms": pre_ms},
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": achieved / pk["hbm_gbs"],
+                     "weight_bytes": weight_bytes, "cache_bytes": cache_bytes,
+                     "note": "weights of a step: every layer's mixer, router, shared expert and `top` experts per token of one sequence"},
+        "closest_model": {"model": f"MiniCPM4 with hidden {z['width']}, intermediate {active}, {z['heads']} heads of {z['dim']}, 2 kv heads, {runs} layers",
+                          "decode_tokens_s": batch * 1000.0 / d_ms, "ms_per_step": d_ms, "prefill_tokens_s": PREFILL_TOKENS / (d_pre * 1e-3),
+                          "prefill_ms": d_pre, "roofline_frac": d_achieved / pk["hbm_gbs"], "weight_bytes": d_weights,
+                          "cache_bytes": d_cache, "gpu_launches": d_launches},
+        "kernels": kernels, "clocks": clocks, "gpu_launches": launches,
+    }))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -746,12 +1004,13 @@ def main() -> int:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=FULL_LAYERS, help="layers built (the full model has 32)")
     ap.add_argument("--batch", type=int, default=8)
-    ap.add_argument("--workload", default="dense8b", choices=["dense8b", "half_b", "sparse8b", "reravik"],
+    ap.add_argument("--workload", default="dense8b", choices=["dense8b", "half_b", "sparse8b", "reravik", "mufevik"],
                     help="dense8b: the headline line (8B sizes, batch 8, context 4096); half_b: 0.5B sizes, batch 64, prompts "
                          "uniform in [64, 2048] chunked at 512, decode at context 8192 (256 steps by default); sparse8b: 8B "
                          "sizes with InfLLM-v2, prompts of 16384 and 30000 tokens chunked at 2048, then decode steps; reravik: the Reravik "
-                         "design at --size beside MiniCPM4 of equal sizes, and its kernels alone")
-    ap.add_argument("--size", default="2k", choices=sorted(RERAVIK_SIZES), help="--workload reravik: which layer sizes")
+                         "design at --size beside MiniCPM4 of equal sizes, and its kernels alone; mufevik: the same for the Mufevik design "
+                         "(sizes 1k and 2k)")
+    ap.add_argument("--size", default="2k", choices=sorted(RERAVIK_SIZES), help="--workload reravik / mufevik: which layer sizes")
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 points and the e2e run")
     ap.add_argument("--kernel", default=None, help="time one kernel alone: skinny_gemm, decode_attention, prefill_attention (tcgen05), prefill_attention_mma, gemm_tcgen05; or run eager steps of a 2-layer model for a launch list: decode_step, prefill_step")
     ap.add_argument("--ctx", type=int, default=CONTEXT, help="--kernel: cached tokens per sequence (or prompt tokens)")
@@ -773,6 +1032,11 @@ def main() -> int:
         return workload_sparse8b(a.steps, a.warmup, a.layers)
     if a.workload == "reravik":
         return workload_reravik(a.steps, max(3, a.warmup), a.size, a.batch)
+    if a.workload == "mufevik":
+        if a.size not in MUFEVIK_SIZES:
+            print(f"bench.py: --workload mufevik takes --size {' or '.join(sorted(MUFEVIK_SIZES))}")
+            return 2
+        return workload_mufevik(a.steps, max(3, a.warmup), a.size, a.batch)
     if a.kernel:
         return kernel_bench(a.kernel, a.batch, a.ctx, a.rows, a.n, a.k, a.reps)
     a.warmup = max(3, a.warmup)

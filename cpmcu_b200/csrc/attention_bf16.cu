@@ -378,7 +378,7 @@ decode_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_c
                         const int* __restrict__ kv_len, const int* __restrict__ slots,
                         const int* __restrict__ page_table, int max_pages, float* __restrict__ part_o,
                         float* __restrict__ part_ml, bf16* __restrict__ out, int n_heads, int n_kv, int m_tiles,
-                        int n_splits, float scale_log2, DecodeRope rope) {
+                        int n_splits, float scale_log2, DecodeRope rope, int v_shift) {
     // A block takes one share of a sequence's pages; its warps take every third page of the
     // share and merge their results in shared memory before anything is written.  With one share
     // per sequence the block writes the final result to ``out`` itself and no combine kernel follows.
@@ -406,7 +406,9 @@ decode_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_c
         const int p = p0 + warp + k * DecodeSmem<D>::kWarps;
         if (p < p1) {
             const int64_t base = (int64_t)CPM_PAGE(pages, p, max_pages) * page_elems + (int64_t)kvh * kPageTokens * D;
-            copy_page_async<D>(my_stages + (k % kDecodeStages) * S::kStageBytes, k_cache + base, v_cache + base, lane);
+            // v_shift: the values come from key-value head (kvh + v_shift) mod n_kv (0: the keys' own head)
+            const int64_t vbase = base + (int64_t)((kvh + v_shift) % n_kv - kvh) * kPageTokens * D;
+            copy_page_async<D>(my_stages + (k % kDecodeStages) * S::kStageBytes, k_cache + base, v_cache + vbase, lane);
         }
         cp_async_commit();
     };
@@ -560,7 +562,7 @@ template <int D>
 static int launch_decode(const void* q, const void* k_cache, const void* v_cache, void* out, const int* kv_len,
                          const int* slots, const int* page_table, int max_pages, float* scratch, int n_seqs,
                          int n_heads, int n_kv, int n_splits, float scale, cudaStream_t stream,
-                         DecodeRope rope = DecodeRope{nullptr, nullptr, 1.f, 0, nullptr, nullptr, 0}) {
+                         DecodeRope rope = DecodeRope{nullptr, nullptr, 1.f, 0, nullptr, nullptr, 0}, int v_shift = 0) {
     const int m_tiles = (n_heads / n_kv + 15) / 16;
     float* part_o = scratch;
     float* part_ml = scratch + (int64_t)n_seqs * n_kv * m_tiles * n_splits * 16 * D;
@@ -572,7 +574,7 @@ static int launch_decode(const void* q, const void* k_cache, const void* v_cache
     if (int st = ensure_dynamic_smem(kern, smem, configured)) return st;
     cpm_launch(kLaunchAttention, kern, grid, DecodeSmem<D>::kWarps * 32, smem, stream, (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache,
                kv_len, slots, page_table, max_pages, part_o, part_ml, (bf16*)out, n_heads, n_kv, m_tiles, n_splits,
-               scale * 1.4426950408889634f, rope);
+               scale * 1.4426950408889634f, rope, v_shift);
     if (n_splits > 1)
         cpm_launch(kLaunchCombine, combine_splits_kernel, dim3(n_heads, n_seqs), D >= 128 ? 128 : 64, 0, stream, (const float*)part_o,
                    (const float*)part_ml, (bf16*)out, n_heads, n_kv, m_tiles, n_splits, (int)D);
@@ -591,6 +593,24 @@ CPM_API int cpm_decode_attention_bf16(const void* q, const void* k_cache, const 
         case 64: return launch_decode<64>(q, k_cache, v_cache, out, kv_len, slots, page_table, max_pages, scratch, n_seqs, n_heads, n_kv, n_splits, scale, stream);
         case 96: return launch_decode<96>(q, k_cache, v_cache, out, kv_len, slots, page_table, max_pages, scratch, n_seqs, n_heads, n_kv, n_splits, scale, stream);
         case 128: return launch_decode<128>(q, k_cache, v_cache, out, kv_len, slots, page_table, max_pages, scratch, n_seqs, n_heads, n_kv, n_splits, scale, stream);
+        default: return CPM_BAD_ARGUMENT;
+    }
+}
+
+// The same with the values taken from key-value head (kv head + v_shift) mod n_kv: a query head's softmax weights
+// over its own keys applied to another head's values (what a mix of the weights across heads needs).
+CPM_API int cpm_decode_attention_bf16_vshift(const void* q, const void* k_cache, const void* v_cache, void* out,
+                                             const int* kv_len, const int* slots, const int* page_table, int max_pages,
+                                             float* scratch, int n_seqs, int n_heads, int n_kv, int d, int n_splits,
+                                             float scale, int v_shift, cudaStream_t stream) {
+    if (n_seqs <= 0) return CPM_OK;
+    if (n_kv <= 0 || n_heads % n_kv || n_splits < 1 || n_seqs > 65535 || !scratch || v_shift < 0 || v_shift >= n_kv) return CPM_BAD_ARGUMENT;
+    const DecodeRope none{nullptr, nullptr, 1.f, 0, nullptr, nullptr, 0};
+    switch (d) {
+        case 32: return launch_decode<32>(q, k_cache, v_cache, out, kv_len, slots, page_table, max_pages, scratch, n_seqs, n_heads, n_kv, n_splits, scale, stream, none, v_shift);
+        case 64: return launch_decode<64>(q, k_cache, v_cache, out, kv_len, slots, page_table, max_pages, scratch, n_seqs, n_heads, n_kv, n_splits, scale, stream, none, v_shift);
+        case 96: return launch_decode<96>(q, k_cache, v_cache, out, kv_len, slots, page_table, max_pages, scratch, n_seqs, n_heads, n_kv, n_splits, scale, stream, none, v_shift);
+        case 128: return launch_decode<128>(q, k_cache, v_cache, out, kv_len, slots, page_table, max_pages, scratch, n_seqs, n_heads, n_kv, n_splits, scale, stream, none, v_shift);
         default: return CPM_BAD_ARGUMENT;
     }
 }
@@ -1014,7 +1034,7 @@ __global__ void __launch_bounds__(kPrefillWarps * 32, 2)
 prefill_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
                          bf16* __restrict__ out, const int* __restrict__ tile_seq, const int* __restrict__ tile_row,
                          const int* __restrict__ cu_q, const int* __restrict__ kv_len, const int* __restrict__ slots,
-                         const int* __restrict__ page_table, int max_pages, int n_heads, int n_kv, float scale_log2) {
+                         const int* __restrict__ page_table, int max_pages, int n_heads, int n_kv, float scale_log2, int v_shift) {
     using S = DecodeSmem<D>;
     extern __shared__ __align__(128) unsigned char smem_raw[];
     const uint32_t stages = (uint32_t)__cvta_generic_to_shared(smem_raw);
@@ -1035,7 +1055,8 @@ prefill_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_
     auto issue = [&](int p) {
         if (p <= last_page) {
             const int64_t base = (int64_t)CPM_PAGE(pages, p, max_pages) * page_elems + (int64_t)kvh * kPageTokens * D;
-            copy_page_async<D, kPrefillWarps * 32>(stages + (p & 1) * S::kStageBytes, k_cache + base, v_cache + base,
+            const int64_t vbase = base + (int64_t)((kvh + v_shift) % n_kv - kvh) * kPageTokens * D;      // see the decode kernel
+            copy_page_async<D, kPrefillWarps * 32>(stages + (p & 1) * S::kStageBytes, k_cache + base, v_cache + vbase,
                                                    threadIdx.x);
         }
         cp_async_commit();
@@ -1086,14 +1107,14 @@ template <int D>
 static int launch_prefill(const void* q, const void* k_cache, const void* v_cache, void* out, const int* tile_seq,
                           const int* tile_row, int n_tiles, const int* cu_q, const int* kv_len, const int* slots,
                           const int* page_table, int max_pages, int n_heads, int n_kv, float scale,
-                          cudaStream_t stream) {
+                          cudaStream_t stream, int v_shift = 0) {
     auto kern = prefill_attention_kernel<D>;
     constexpr int smem = 2 * DecodeSmem<D>::kStageBytes;
     static bool configured[kMaxDevices] = {};            // per kernel and per device
     if (int st = ensure_dynamic_smem(kern, smem, configured)) return st;
     kern<<<dim3(n_heads, n_tiles), kPrefillWarps * 32, smem, stream>>>((const bf16*)q, (const bf16*)k_cache,
         (const bf16*)v_cache, (bf16*)out, tile_seq, tile_row, cu_q, kv_len, slots, page_table, max_pages, n_heads, n_kv,
-        scale * 1.4426950408889634f);
+        scale * 1.4426950408889634f, v_shift);
     return launch_status();
 }
 
@@ -1109,6 +1130,22 @@ CPM_API int cpm_prefill_attention_bf16(const void* q, const void* k_cache, const
         case 64: return launch_prefill<64>(q, k_cache, v_cache, out, tile_seq, tile_row, n_tiles, cu_q, kv_len, slots, page_table, max_pages, n_heads, n_kv, scale, stream);
         case 96: return launch_prefill<96>(q, k_cache, v_cache, out, tile_seq, tile_row, n_tiles, cu_q, kv_len, slots, page_table, max_pages, n_heads, n_kv, scale, stream);
         case 128: return launch_prefill<128>(q, k_cache, v_cache, out, tile_seq, tile_row, n_tiles, cu_q, kv_len, slots, page_table, max_pages, n_heads, n_kv, scale, stream);
+        default: return CPM_BAD_ARGUMENT;
+    }
+}
+
+// The same with the values taken from key-value head (kv head + v_shift) mod n_kv.
+CPM_API int cpm_prefill_attention_bf16_vshift(const void* q, const void* k_cache, const void* v_cache, void* out,
+                                              const int* tile_seq, const int* tile_row, int n_tiles, const int* cu_q,
+                                              const int* kv_len, const int* slots, const int* page_table, int max_pages,
+                                              int n_heads, int n_kv, int d, float scale, int v_shift, cudaStream_t stream) {
+    if (n_tiles <= 0) return CPM_OK;
+    if (n_kv <= 0 || n_heads % n_kv || n_tiles > 65535 || v_shift < 0 || v_shift >= n_kv) return CPM_BAD_ARGUMENT;
+    switch (d) {
+        case 32: return launch_prefill<32>(q, k_cache, v_cache, out, tile_seq, tile_row, n_tiles, cu_q, kv_len, slots, page_table, max_pages, n_heads, n_kv, scale, stream, v_shift);
+        case 64: return launch_prefill<64>(q, k_cache, v_cache, out, tile_seq, tile_row, n_tiles, cu_q, kv_len, slots, page_table, max_pages, n_heads, n_kv, scale, stream, v_shift);
+        case 96: return launch_prefill<96>(q, k_cache, v_cache, out, tile_seq, tile_row, n_tiles, cu_q, kv_len, slots, page_table, max_pages, n_heads, n_kv, scale, stream, v_shift);
+        case 128: return launch_prefill<128>(q, k_cache, v_cache, out, tile_seq, tile_row, n_tiles, cu_q, kv_len, slots, page_table, max_pages, n_heads, n_kv, scale, stream, v_shift);
         default: return CPM_BAD_ARGUMENT;
     }
 }

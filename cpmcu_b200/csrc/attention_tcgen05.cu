@@ -98,7 +98,7 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
                                  const int* __restrict__ cu_q, const int* __restrict__ kv_len,
                                  const int* __restrict__ slots, const int* __restrict__ page_table, int max_pages,
                                  int n_pages, int n_heads, int n_kv, float scale_log2, float* __restrict__ part_o,
-                                 float* __restrict__ part_ml, int n_splits, int n_tokens) {
+                                 float* __restrict__ part_ml, int n_splits, int n_tokens, int v_shift) {
     using Z = Sizes<kD>;
     constexpr int kTileBytes = Z::kTileBytes;
     extern __shared__ unsigned char smem_raw[];
@@ -187,8 +187,9 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
                 }
                 if (!mbar_wait_bounded(smem_u32(&v_empty[s]), ph ^ 1)) { fail(ERR_V_EMPTY); break; }
                 mbar_expect_tx(smem_u32(&v_full[s]), kTileBytes);
-                tma_load_2d(v_smem + s * kTileBytes, &map_v, smem_u32(&v_full[s]), 0, (pa * n_kv + kvh) * kD);
-                tma_load_2d(v_smem + s * kTileBytes + Z::kVPageBytes, &map_v, smem_u32(&v_full[s]), 0, (pb * n_kv + kvh) * kD);
+                const int vh = (kvh + v_shift) % n_kv;       // values of another key-value head when v_shift > 0
+                tma_load_2d(v_smem + s * kTileBytes, &map_v, smem_u32(&v_full[s]), 0, (pa * n_kv + vh) * kD);
+                tma_load_2d(v_smem + s * kTileBytes + Z::kVPageBytes, &map_v, smem_u32(&v_full[s]), 0, (pb * n_kv + vh) * kD);
             }
             if (aborted()) {
                 // copies that nobody consumed: wait for them (bounded), so that none is in flight at the exit
@@ -793,7 +794,7 @@ template <int D>
 static int launch(const void* q, const void* k_cache, const void* v_cache, void* out, const int* tile_seq, const int* tile_row,
                   int n_tiles, const int* cu_q, const int* kv_len, const int* slots, const int* page_table, int max_pages,
                   int n_tokens, int n_pages, int n_heads, int n_kv, float scale, float* scratch, int n_splits,
-                  cudaStream_t stream) {
+                  cudaStream_t stream, int v_shift = 0) {
     CUtensorMap map_q, map_k, map_v;
     if (!tc5::make_map_2d_bf16(&map_q, q, (uint64_t)n_tokens, (uint64_t)n_heads * D, (uint64_t)n_heads * D * 2, 64, kTileRows) ||
         !tc5::make_map_2d_bf16(&map_k, k_cache, (uint64_t)n_pages * n_kv * kPageTokens, D, D * 2, 64, kPageTokens) ||
@@ -806,7 +807,7 @@ static int launch(const void* q, const void* k_cache, const void* v_cache, void*
     float* part_ml = scratch ? scratch + (int64_t)n_splits * n_tokens * n_heads * D : nullptr;
     kern<<<dim3(n_heads / 2, n_tiles, n_splits), kThreads, Sizes<D>::kSmemBytes, stream>>>(map_q, map_k, map_v, (bf16*)out,
         tile_seq, tile_row, cu_q, kv_len, slots, page_table, max_pages, n_pages, n_heads, n_kv, scale * 1.4426950408889634f,
-        part_o, part_ml, n_splits, n_tokens);
+        part_o, part_ml, n_splits, n_tokens, v_shift);
     if (n_splits > 1)
         combine_key_shares_kernel<<<dim3(n_tokens, n_heads), D / 2, 0, stream>>>(part_o, part_ml, (bf16*)out, n_tokens, n_heads,
                                                                                D, n_splits);
@@ -834,6 +835,25 @@ CPM_API int cpm_prefill_attention_tcgen05(const void* q, const void* k_cache, co
                                 n_tokens, n_pages, n_heads, n_kv, scale, scratch, n_splits, stream);
     return fa5::launch<64>(q, k_cache, v_cache, out, tile_seq, tile_row, n_tiles, cu_q, kv_len, slots, page_table, max_pages,
                            n_tokens, n_pages, n_heads, n_kv, scale, scratch, n_splits, stream);
+}
+
+// The same with the values taken from key-value head (kv head + v_shift) mod n_kv.
+CPM_API int cpm_prefill_attention_tcgen05_vshift(const void* q, const void* k_cache, const void* v_cache, void* out,
+                                                 const int* tile_seq, const int* tile_row, int n_tiles, const int* cu_q,
+                                                 const int* kv_len, const int* slots, const int* page_table, int max_pages,
+                                                 int n_tokens, int n_pages, int n_heads, int n_kv, int d, float scale,
+                                                 float* scratch, int n_splits, int v_shift, cudaStream_t stream) {
+    if (n_tiles <= 0 || n_tokens <= 0) return CPM_OK;
+    if (n_splits < 1 || n_splits > 64 || (n_splits > 1 && !scratch) || n_tokens > 65535 * 1024) return CPM_BAD_ARGUMENT;
+    if ((d != 128 && d != 64) || n_kv <= 0 || n_heads % n_kv || (n_heads / n_kv) % 2 || n_tiles > 65535 || n_pages <= 0 ||
+        v_shift < 0 || v_shift >= n_kv ||
+        ((uintptr_t)q & 15) || ((uintptr_t)k_cache & 15) || ((uintptr_t)v_cache & 15) || ((uintptr_t)out & 15))
+        return CPM_BAD_ARGUMENT;
+    if (d == 128)
+        return fa5::launch<128>(q, k_cache, v_cache, out, tile_seq, tile_row, n_tiles, cu_q, kv_len, slots, page_table, max_pages,
+                                n_tokens, n_pages, n_heads, n_kv, scale, scratch, n_splits, stream, v_shift);
+    return fa5::launch<64>(q, k_cache, v_cache, out, tile_seq, tile_row, n_tiles, cu_q, kv_len, slots, page_table, max_pages,
+                           n_tokens, n_pages, n_heads, n_kv, scale, scratch, n_splits, stream, v_shift);
 }
 
 // Block-list attention of prompt tokens on the tensor cores (see listed_attention_tcgen05_kernel): q, out [tokens, heads,

@@ -156,4 +156,69 @@ CPM_API int cpm_talking_attention(const void* q, const void* k_cache, const void
     return launch_status();
 }
 
+// ---------------------------------------------------------------------------
+// The same attention from the tensor-core kernels of plain softmax attention.  The mix is linear in the weights, so
+//   o_h = sum_g talk[h][g] * A[g][kv(h)],     A[g][c] = sum_j p_g(j) v_c(j)
+// and A[.][(kv(g) + s) mod n_kv] for all g is what one run of a plain attention kernel gives whose values come from
+// the key-value head s places after the keys' (its ``v_shift``).  n_kv runs, s = 0 .. n_kv - 1, then this mix.  The
+// temperature goes into the queries beforehand (scale_heads).
+// ---------------------------------------------------------------------------
+__global__ void scale_heads_kernel(const bf16* __restrict__ q, const float* __restrict__ temp, bf16* __restrict__ out, int n_heads,
+                                   int d) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int64_t t = blockIdx.x;
+    for (int i = threadIdx.x; i < n_heads * d; i += blockDim.x)
+        out[t * n_heads * d + i] = __float2bfloat16_rn(__bfloat162float(q[t * n_heads * d + i]) * temp[i / d]);
+}
+
+// parts [n_kv][tokens][heads][d] (run s at parts[s]) -> out [tokens][heads][d]
+__global__ void talk_mix_kernel(const bf16* __restrict__ parts, const float* __restrict__ talk, bf16* __restrict__ out,
+                                int64_t n_tokens, int n_heads, int n_kv, int d) {
+    extern __shared__ float mix_smem[];          // [n_kv][heads][d] of this token, then talk [heads][heads]
+    float* tk = mix_smem + n_kv * n_heads * d;
+    pdl_launch_dependents();
+    for (int i = threadIdx.x; i < n_heads * n_heads; i += blockDim.x) tk[i] = talk[i];
+    pdl_wait();
+    const int64_t t = blockIdx.x;
+    const int row = n_heads * d;
+    for (int i = threadIdx.x; i < n_kv * row; i += blockDim.x)
+        mix_smem[i] = __bfloat162float(parts[((int64_t)(i / row) * n_tokens + t) * row + i % row]);
+    __syncthreads();
+    const int rep = n_heads / n_kv;
+    for (int i = threadIdx.x; i < row; i += blockDim.x) {
+        const int h = i / d, c = i % d;
+        float acc = 0.f;
+        for (int g = 0; g < n_heads; ++g) {
+            const int s = (h / rep - g / rep + n_kv) % n_kv;          // the run in which head g saw the values of h's head
+            acc = fmaf(tk[h * n_heads + g], mix_smem[(s * n_heads + g) * d + c], acc);
+        }
+        out[t * row + i] = __float2bfloat16_rn(acc);
+    }
+}
+
+CPM_API int cpm_scale_heads_bf16(const void* q, const float* temp, void* out, int n_tokens, int n_heads, int d, cudaStream_t stream) {
+    if (n_tokens <= 0) return CPM_OK;
+    cpm_launch(kLaunchRope, scale_heads_kernel, dim3(n_tokens), dim3(n_heads * d >= 1024 ? 256 : 128), 0, stream, (const bf16*)q, temp,
+               (bf16*)out, n_heads, d);
+    return launch_status();
+}
+
+static bool g_mix_smem_done[kMaxDevices];
+
+CPM_API int cpm_talk_mix_bf16(const void* parts, const float* talk, void* out, int n_tokens, int n_heads, int n_kv, int d,
+                              cudaStream_t stream) {
+    if (n_tokens <= 0) return CPM_OK;
+    if (n_heads < 1 || n_kv < 1 || n_heads % n_kv) return CPM_BAD_ARGUMENT;
+    const size_t smem = (size_t)(n_kv * n_heads * d + n_heads * n_heads) * sizeof(float);
+    if (smem > 200 * 1024) return CPM_BAD_ARGUMENT;
+    if (smem > 48 * 1024) {
+        const int e = ensure_dynamic_smem(talk_mix_kernel, 200 * 1024, g_mix_smem_done);
+        if (e != CPM_OK) return e;
+    }
+    cpm_launch(kLaunchCombine, talk_mix_kernel, dim3(n_tokens), dim3(256), smem, stream, (const bf16*)parts, talk, (bf16*)out,
+               (int64_t)n_tokens, n_heads, n_kv, d);
+    return launch_status();
+}
+
 CPM_BOUNDS_TU(talking_attention)

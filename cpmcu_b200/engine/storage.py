@@ -17,7 +17,7 @@ import torch
 from ..cache import Cache, PAGE_TOKENS
 from ..memory import ALIGN, Arena, PoolExhausted, Workspace, plan_storage, round_up
 from ..models.model import Model
-from ..ops.dry import measure_workspace
+from ..ops.dry import measure_weights, measure_workspace
 from .decode import bucket_size
 
 
@@ -43,7 +43,8 @@ def weight_bytes(model: Model) -> int:
         for s in spec.shape:
             n *= s
         total += round_up(n * (es if spec.role == "matrix" else 4))
-    return total + 64 * ALIGN
+    # parts may keep fused or widened copies that the declared shapes do not show: count what they keep
+    return max(total, measure_weights(model.spec, model.ops.dtype)) + 64 * ALIGN
 
 
 def make_storage(model: Model, chunk_tokens: int, max_batch: int, max_tokens: Optional[int] = None,

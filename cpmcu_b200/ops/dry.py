@@ -81,8 +81,28 @@ class DryOps(Ops):
     def set_page_limit(self, n_pages):
         pass
 
+    kept_bytes = 0      # what the parts asked to keep for good, each tensor rounded up to the arena's alignment
+
+    def keep(self, t):
+        from ..memory import round_up
+        self.kept_bytes += round_up(t.numel() * t.element_size())
+        return t
+
     def result(self, *shape, dtype=None):
         return torch.empty(*shape, dtype=dtype or self.dtype, device="meta")
+
+
+def measure_weights(spec, dtype: torch.dtype) -> int:
+    """Bytes of the tensors a model's parts keep for good once loaded (fused and widened copies included, which the
+    declared shapes do not show), counted by loading tensors without storage; vectors as 32-bit, the most they can be."""
+    from ..models.model import Model
+
+    ops = DryOps(dtype)
+    model = Model(spec, ops)
+    model.load_weights({name: torch.empty(w.shape, device="meta",
+                                          dtype=torch.int32 if w.role == "table" else (dtype if w.role == "matrix" else torch.float32))
+                        for name, w in model.weight_specs().items()})
+    return ops.kept_bytes
 
 
 def _meta(n: int) -> torch.Tensor:

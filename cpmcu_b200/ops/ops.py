@@ -607,19 +607,27 @@ class Ops:
 
     def decode_attention(self, q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, kv_len: torch.Tensor,
                          slots: torch.Tensor, page_table: torch.Tensor, n_kv: int, scale: float,
-                         n_splits: Optional[int] = None) -> torch.Tensor:
-        """One query token per sequence: q [seqs, heads, d] -> [seqs, heads*d]."""
+                         n_splits: Optional[int] = None, out: Optional[torch.Tensor] = None, v_shift: int = 0) -> torch.Tensor:
+        """One query token per sequence: q [seqs, heads, d] -> [seqs, heads*d].  ``v_shift``: the values come from
+        key-value head (kv head + v_shift) mod n_kv instead of the keys' own."""
         self._act(q, "q")
         n, n_heads, d = q.shape
         if n_splits is None:
             n_splits = self.decode_splits(n, n_heads, n_kv)
         floats = self.lib.cpm_decode_attention_scratch_floats(n, n_heads, n_kv, d, n_splits)
         scratch = self.empty(floats, dtype=torch.float32)
-        out = self.empty(n, n_heads * d)
-        check(self.lib.cpm_decode_attention_bf16(_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(kv_len),
-                                                 _ptr(slots), _ptr(page_table), page_table.shape[1], _ptr(scratch),
-                                                 n, n_heads, n_kv, d, n_splits, float(scale), self._stream()),
-              f"decode attention (head_dim {d})")
+        if out is None:
+            out = self.empty(n, n_heads * d)
+        if v_shift:
+            check(self.lib.cpm_decode_attention_bf16_vshift(_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(kv_len),
+                                                            _ptr(slots), _ptr(page_table), page_table.shape[1], _ptr(scratch),
+                                                            n, n_heads, n_kv, d, n_splits, float(scale), int(v_shift), self._stream()),
+                  f"decode attention (head_dim {d}, values shifted)")
+        else:
+            check(self.lib.cpm_decode_attention_bf16(_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(kv_len),
+                                                     _ptr(slots), _ptr(page_table), page_table.shape[1], _ptr(scratch),
+                                                     n, n_heads, n_kv, d, n_splits, float(scale), self._stream()),
+                  f"decode attention (head_dim {d})")
         if n_splits > 1:
             LAUNCHES_EXTRA[0] += 1       # the launcher starts two kernels: the shares, then their combination
         return out
@@ -667,35 +675,40 @@ class Ops:
 
     def prefill_attention(self, q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, tiles,
                           cu_q: torch.Tensor, kv_len: torch.Tensor, slots: torch.Tensor, page_table: torch.Tensor,
-                          n_kv: int, scale: float) -> torch.Tensor:
+                          n_kv: int, scale: float, out: Optional[torch.Tensor] = None, v_shift: int = 0) -> torch.Tensor:
         """q [tokens, heads, d] packed by sequence -> [tokens, heads*d]; tiles = (tile_seq, tile_row, count)
-        lists the query tiles of PREFILL_TILE_ROWS tokens."""
+        lists the query tiles of PREFILL_TILE_ROWS tokens.  ``v_shift``: as in ``decode_attention``."""
         self._act(q, "q")
         n, n_heads, d = q.shape
         tile_seq, tile_row, n_tiles = tiles
-        out = self.empty(n, n_heads * d)
-        check(self.lib.cpm_prefill_attention_bf16(_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(tile_seq),
-                                                  _ptr(tile_row), n_tiles, _ptr(cu_q), _ptr(kv_len), _ptr(slots),
-                                                  _ptr(page_table), page_table.shape[1], n_heads, n_kv, d,
-                                                  float(scale), self._stream()), f"prefill attention (head_dim {d})")
+        if out is None:
+            out = self.empty(n, n_heads * d)
+        check(self.lib.cpm_prefill_attention_bf16_vshift(_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(tile_seq),
+                                                         _ptr(tile_row), n_tiles, _ptr(cu_q), _ptr(kv_len), _ptr(slots),
+                                                         _ptr(page_table), page_table.shape[1], n_heads, n_kv, d,
+                                                         float(scale), int(v_shift), self._stream()),
+              f"prefill attention (head_dim {d})")
         return out
 
 
     def prefill_attention_tcgen05(self, q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, tiles,
                                   cu_q: torch.Tensor, kv_len: torch.Tensor, slots: torch.Tensor,
-                                  page_table: torch.Tensor, n_kv: int, scale: float, n_splits: int = 1) -> torch.Tensor:
+                                  page_table: torch.Tensor, n_kv: int, scale: float, n_splits: int = 1,
+                                  out: Optional[torch.Tensor] = None, v_shift: int = 0) -> torch.Tensor:
         """The same as ``prefill_attention`` on the tcgen05 tensor cores: head size 128 or 64 and an even number
         of query heads per key/value head.  ``n_splits`` > 1 shares the keys of every tile out over that many
         blocks (a short chunk after a long history would otherwise keep few SMs busy for long)."""
         self._act(q, "q")
         n, n_heads, d = q.shape
         tile_seq, tile_row, n_tiles = tiles
-        out = self.empty(n, n_heads * d)
+        if out is None:
+            out = self.empty(n, n_heads * d)
         scratch = self.empty(n_splits * n * n_heads * (d + 2), dtype=torch.float32) if n_splits > 1 else None
-        check(self.lib.cpm_prefill_attention_tcgen05(_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(tile_seq),
-                                                     _ptr(tile_row), n_tiles, _ptr(cu_q), _ptr(kv_len), _ptr(slots),
-                                                     _ptr(page_table), page_table.shape[1], n, k_cache.shape[0],
-                                                     n_heads, n_kv, d, float(scale), _ptr(scratch), n_splits, self._stream()),
+        check(self.lib.cpm_prefill_attention_tcgen05_vshift(_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(tile_seq),
+                                                            _ptr(tile_row), n_tiles, _ptr(cu_q), _ptr(kv_len), _ptr(slots),
+                                                            _ptr(page_table), page_table.shape[1], n, k_cache.shape[0],
+                                                            n_heads, n_kv, d, float(scale), _ptr(scratch), n_splits,
+                                                            int(v_shift), self._stream()),
               f"tcgen05 prefill attention (head_dim {d})")
         return out
 
@@ -872,11 +885,52 @@ class Ops:
                                          n, n_heads, n_kv, d, dv, int(rot_dim), self.code, self._stream()), "rope_store_dv")
         return q
 
+    TALKING_MAX_RUNS = 8      # most key-value heads for which the mix is built from runs of the plain attention kernels
+
+    def talking_attention_on_tensor_cores(self, ctx, n_heads: int, n_kv: int, d: int, dv: int) -> bool:
+        """bf16, equal key and value sizes that the tensor-core attention kernels are built for, few key-value heads, and
+        a step they take (one token per sequence, or prompt tokens with query tiles)."""
+        return (self.code == BF16 and d == dv and d in FAST_HEAD_DIMS and n_kv <= self.TALKING_MAX_RUNS
+                and (ctx.is_decode or ctx.q_tiles is not None) and os.environ.get("CPMCU_TALKING_GENERIC", "0") != "1")
+
     def talking_attention(self, ctx, q: torch.Tensor, lane, n_kv: int, dv: int, scale: float, temp: torch.Tensor,
                           talk: torch.Tensor) -> torch.Tensor:
         """Causal softmax attention over the lane's cache with scores times ``scale * temp[head]`` and the softmax
         weights mixed across heads by ``talk`` [heads, heads] (row: the head that receives); q [tokens, heads, d] ->
-        [tokens, heads*dv]."""
+        [tokens, heads*dv].  Picks the kernels: the mix is linear in the weights, o_h = sum_g talk[h][g] A[g][kv(h)] with
+        A[g][c] head g's weights applied to the values of key-value head c, so n_kv runs of the plain tensor-core
+        attention (run s reading the values s heads after the keys') and one mixing kernel give it; sizes and steps
+        those kernels do not take, and the 32-bit path, go to the kernel that forms the mixed weights itself."""
+        n, n_heads, d = q.shape
+        if not self.talking_attention_on_tensor_cores(ctx, n_heads, n_kv, d, dv):
+            return self.talking_attention_generic(ctx, q, lane, n_kv, dv, scale, temp, talk)
+        self._act(q, "q")
+        self._f32(temp, "head temperatures")
+        self._f32(talk, "head mix")
+        qs = self.empty(n, n_heads, d)
+        check(self.lib.cpm_scale_heads_bf16(_ptr(q), _ptr(temp), _ptr(qs), n, n_heads, d, self._stream()), "scale_heads")
+        parts = self.empty(n_kv, n, n_heads * d)
+        tiles = ctx.q_tiles
+        on_tcgen05 = (not ctx.is_decode and self.use_tcgen05_attention and (n_heads // n_kv) % 2 == 0
+                      and (d == 128 or (d == 64 and ctx.max_kv_len >= 1024)))
+        shares = self.prefill_key_shares(ctx.q_lens, ctx.max_kv_len, n_heads) if on_tcgen05 else 1
+        for s in range(n_kv):
+            if ctx.is_decode:
+                self.decode_attention(qs, lane.k, lane.v, ctx.kv_len_dev, ctx.slot_dev, lane.page_table, n_kv, scale,
+                                      out=parts[s], v_shift=s)
+            elif on_tcgen05:
+                self.prefill_attention_tcgen05(qs, lane.k, lane.v, tiles, ctx.cu_q, ctx.kv_len_dev, ctx.slot_dev, lane.page_table,
+                                               n_kv, scale, shares, out=parts[s], v_shift=s)
+            else:
+                self.prefill_attention(qs, lane.k, lane.v, tiles, ctx.cu_q, ctx.kv_len_dev, ctx.slot_dev, lane.page_table, n_kv,
+                                       scale, out=parts[s], v_shift=s)
+        out = self.empty(n, n_heads * d)
+        check(self.lib.cpm_talk_mix_bf16(_ptr(parts), _ptr(talk), _ptr(out), n, n_heads, n_kv, d, self._stream()), "talk_mix")
+        return out
+
+    def talking_attention_generic(self, ctx, q: torch.Tensor, lane, n_kv: int, dv: int, scale: float, temp: torch.Tensor,
+                                  talk: torch.Tensor) -> torch.Tensor:
+        """The kernel that forms the mixed weights itself (two walks over a query's keys), any sizes, both precisions."""
         self._act(q, "q")
         self._f32(temp, "head temperatures")
         self._f32(talk, "head mix")

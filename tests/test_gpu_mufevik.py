@@ -272,18 +272,22 @@ def test_command_line_and_replay(folders, tmp_path):
 
 def _ctx(q_lens, starts, slots):
     """A step's description on the device for sequences that bring ``q_lens`` tokens from positions ``starts``."""
-    from cpmcu_b200.parts.base import StepContext
+    from cpmcu_b200.parts.base import QUERY_TILE_TOKENS, StepContext
 
     i32 = dict(dtype=torch.int32, device="cuda")
     pos = torch.cat([torch.arange(s, s + n) for n, s in zip(q_lens, starts)]).to(**i32)
     seq = torch.cat([torch.full((n,), i) for i, n in enumerate(q_lens)]).to(**i32)
     cu = torch.tensor([0] + list(np.cumsum(q_lens)), **i32)
-    return StepContext(n_tokens=sum(q_lens), n_seqs=len(q_lens), is_decode=all(n == 1 for n in q_lens), captured=False,
-                       q_lens=list(q_lens), kv_lens=[s + n for n, s in zip(q_lens, starts)], slots=list(slots),
-                       max_q_len=max(q_lens), max_kv_len=max(s + n for n, s in zip(q_lens, starts)),
-                       token_ids=torch.zeros(sum(q_lens), **i32), positions=pos, token_seq=seq, cu_q=cu,
-                       kv_len_dev=torch.tensor([s + n for n, s in zip(q_lens, starts)], **i32),
-                       slot_dev=torch.tensor(list(slots), **i32))
+    ctx = StepContext(n_tokens=sum(q_lens), n_seqs=len(q_lens), is_decode=all(n == 1 for n in q_lens), captured=False,
+                      q_lens=list(q_lens), kv_lens=[s + n for n, s in zip(q_lens, starts)], slots=list(slots),
+                      max_q_len=max(q_lens), max_kv_len=max(s + n for n, s in zip(q_lens, starts)),
+                      token_ids=torch.zeros(sum(q_lens), **i32), positions=pos, token_seq=seq, cu_q=cu,
+                      kv_len_dev=torch.tensor([s + n for n, s in zip(q_lens, starts)], **i32),
+                      slot_dev=torch.tensor(list(slots), **i32))
+    ts = [i for i, n in enumerate(q_lens) for _ in range(0, n, QUERY_TILE_TOKENS)]
+    trow = [r for n in q_lens for r in range(0, n, QUERY_TILE_TOKENS)]
+    ctx.q_tiles = (torch.tensor(ts, **i32), torch.tensor(trow, **i32), len(ts))
+    return ctx
 
 
 def _close(got, want, dtype, tol32=2e-5, tol16=2e-2):
@@ -339,13 +343,16 @@ def _attention_reference(q, k, v, temp, talk, scale, rot):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("generic", [True, False])
 @pytest.mark.parametrize("H,G,d,dv,rot", [(4, 2, 24, 40, (16, 5000.0)), (5, 5, 12, 36, (6, 777.0)), (1, 1, 64, 64, (64, 10000.0)),
-                                          (6, 3, 8, 12, None), (32, 8, 128, 128, (64, 1e6))])
-def test_talking_attention_sees_every_key_up_to_the_query_and_mixes_heads(dtype, H, G, d, dv, rot):
+                                          (6, 3, 8, 12, None), (32, 8, 128, 128, (64, 1e6)), (8, 4, 64, 64, (32, 1e4)),
+                                          (6, 3, 96, 96, None), (3, 3, 32, 32, (32, 50.0))])
+def test_talking_attention_sees_every_key_up_to_the_query_and_mixes_heads(dtype, H, G, d, dv, rot, generic):
     """For chosen (query, key) pairs one score towers over the others: the first key, a key far back, the keys on both
     sides of a page border and the query itself; right after the query stands a still larger key that must stay
     unseen.  The towering part lies in dimensions that are not rotated where there are any.  Run as one prompt and as a
-    prompt followed by single tokens, in slots and pages that are not the first."""
+    prompt followed by single tokens, in slots and pages that are not the first; by the kernel that forms the mixed
+    weights itself, and by the choice the library makes (runs of the tensor-core attention and a mix, where they fit)."""
     from cpmcu_b200.cache import Cache
     from cpmcu_b200.ops.ops import Ops
     from cpmcu_b200.parts.base import CacheNeeds
@@ -387,7 +394,8 @@ def test_talking_attention_sees_every_key_up_to_the_query_and_mixes_heads(dtype,
             cache.sync()
             ctx = _ctx([n], [at], [slot])
             qr = ops.rope_store_dv(ctx, qkv[at:at + n].contiguous(), lane, H, G, d, dv, inv_freq, rot[0] if rot else 0)
-            outs.append(ops.talking_attention(ctx, qr, lane, G, dv, scale, temp.cuda(), talk.cuda()))
+            fn = ops.talking_attention_generic if generic else ops.talking_attention
+            outs.append(fn(ctx, qr, lane, G, dv, scale, temp.cuda(), talk.cuda()))
             at += n
         got = torch.cat(outs)
         _close(got, want, dtype, tol32=3e-5, tol16=3e-2)
