@@ -13,12 +13,12 @@
 
 constexpr int kMaxStreams = 16;
 
-template <typename T>
+template <typename T, int NS>      // NS: a compile-time bound on the streams (the loops are unrolled to it)
 __global__ void hyper_step_kernel(float* __restrict__ X, const T* __restrict__ y, const float* __restrict__ mix,
                                   const float* __restrict__ out_w, const float* __restrict__ in_w,
                                   const float* __restrict__ gain, float eps, T* __restrict__ h,
                                   float* __restrict__ total, int S, int W) {
-    __shared__ float s_mix[kMaxStreams * kMaxStreams], s_out[kMaxStreams], s_in[kMaxStreams], scratch[33];
+    __shared__ float s_mix[NS * NS], s_out[NS], s_in[NS], scratch[33];
     pdl_launch_dependents();
     for (int i = threadIdx.x; i < S * S; i += blockDim.x) s_mix[i] = y ? mix[i] : 0.f;
     for (int i = threadIdx.x; i < S; i += blockDim.x) {
@@ -31,18 +31,18 @@ __global__ void hyper_step_kernel(float* __restrict__ X, const T* __restrict__ y
     float* xt = X + t * S * W;
     float ss = 0.f;
     for (int c = threadIdx.x; c < W; c += blockDim.x) {
-        float old[kMaxStreams];
+        float old[NS];
 #pragma unroll
-        for (int s = 0; s < kMaxStreams; ++s) old[s] = s < S ? xt[(int64_t)s * W + c] : 0.f;
+        for (int s = 0; s < NS; ++s) old[s] = s < S ? xt[(int64_t)s * W + c] : 0.f;
         float u = 0.f, sum = 0.f;
         if (y) {
             const float yc = to_f32(y[t * W + c]);
 #pragma unroll
-            for (int r = 0; r < kMaxStreams; ++r) {
+            for (int r = 0; r < NS; ++r) {
                 if (r < S) {
                     float v = 0.f;
 #pragma unroll
-                    for (int s = 0; s < kMaxStreams; ++s)
+                    for (int s = 0; s < NS; ++s)
                         if (s < S) v = fmaf(s_mix[s * S + r], old[s], v);
                     v = fmaf(s_out[r], yc, v);
                     xt[(int64_t)r * W + c] = v;
@@ -52,7 +52,7 @@ __global__ void hyper_step_kernel(float* __restrict__ X, const T* __restrict__ y
             }
         } else {
 #pragma unroll
-            for (int r = 0; r < kMaxStreams; ++r)
+            for (int r = 0; r < NS; ++r)
                 if (r < S) {
                     u = fmaf(s_in[r], old[r], u);
                     sum += old[r];
@@ -92,12 +92,20 @@ CPM_API int cpm_hyper_step(float* X, const void* y, const float* mix, const floa
     if (y && (!mix || !out_w)) return CPM_BAD_ARGUMENT;
     if (in_w && (!gain || !h)) return CPM_BAD_ARGUMENT;
     const int threads = W >= 1024 ? 256 : 128;
-    if (dtype == CPM_BF16)
-        cpm_launch(kLaunchNorm, hyper_step_kernel<bf16>, dim3(n_tokens), dim3(threads), 0, stream, X, (const bf16*)y, mix, out_w, in_w,
-                   gain, eps, (bf16*)h, total, S, W);
-    else
-        cpm_launch(kLaunchNorm, hyper_step_kernel<float>, dim3(n_tokens), dim3(threads), 0, stream, X, (const float*)y, mix, out_w,
-                   in_w, gain, eps, (float*)h, total, S, W);
+#define CPM_HYPER(NS)                                                                                                              \
+    do {                                                                                                                           \
+        if (dtype == CPM_BF16)                                                                                                     \
+            cpm_launch(kLaunchNorm, hyper_step_kernel<bf16, NS>, dim3(n_tokens), dim3(threads), 0, stream, X, (const bf16*)y, mix,  \
+                       out_w, in_w, gain, eps, (bf16*)h, total, S, W);                                                             \
+        else                                                                                                                       \
+            cpm_launch(kLaunchNorm, hyper_step_kernel<float, NS>, dim3(n_tokens), dim3(threads), 0, stream, X, (const float*)y,     \
+                       mix, out_w, in_w, gain, eps, (float*)h, total, S, W);                                                       \
+    } while (0)
+    if (S <= 2) CPM_HYPER(2);
+    else if (S <= 4) CPM_HYPER(4);
+    else if (S <= 8) CPM_HYPER(8);
+    else CPM_HYPER(16);
+#undef CPM_HYPER
     return launch_status();
 }
 

@@ -11,7 +11,8 @@
 //
 // Every value column of S is independent of the others, so a column belongs to kLanes threads that split the
 // key channels among them (registers), and a block holds kCols columns of one head and sequence and walks the
-// sequence's tokens of the step.  Query and key head of value head h: h / (heads / qk_heads).
+// sequence's tokens of the step, whose operands arrive eight tokens at a time in one of two shared-memory buffers
+// (asynchronous copies, the next eight on their way while these are worked).  Query and key head of value head h: h / (heads / qk_heads).
 //
 // Around it: the short causal convolution over time with SiLU, the unit-length scaling of q and k, the gates of
 // the delta rule, the decay of the gated linear attention, and the per-head RMS norm of the read-out times the
@@ -25,6 +26,17 @@ __device__ __forceinline__ float softplus_acc(float v) { return fmaxf(v, 0.f) + 
 
 constexpr int kLanes = 8;      // threads that share one value column
 constexpr int kCols = 32;      // value columns per block
+constexpr int kRecTile = 8;    // tokens whose operands are staged in shared memory at a time
+
+__device__ __forceinline__ void cp_async_f32(float* smem_dst, const float* gmem_src) {
+    const uint32_t dst = (uint32_t)__cvta_generic_to_shared(smem_dst);
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" :: "r"(dst), "l"(gmem_src) : "memory");
+}
+
+// Floats of one staging buffer: q and k [tile][d], the decay [tile][d] or [tile], v [tile][kCols], beta [tile].
+static inline int recurrence_stage_floats(int d, bool vector_decay) {
+    return kRecTile * (2 * d + (vector_decay ? d : 1) + kCols + 1);
+}
 
 template <int PER, bool DELTA, bool VECTOR_DECAY>
 __global__ void __launch_bounds__(kLanes * kCols)
@@ -35,10 +47,12 @@ linear_recurrence_kernel(const float* __restrict__ q, const float* __restrict__ 
                          float* __restrict__ state, const int* __restrict__ positions, const int* __restrict__ cu_q,
                          const int* __restrict__ slots, float* __restrict__ out,                           // [tokens, heads, dv]
                          int heads, int qk_heads, int d, int dv, float q_scale) {
+    extern __shared__ float rec_smem[];
     pdl_launch_dependents();
     pdl_wait();
     const int lane = threadIdx.x % kLanes;
-    const int col = blockIdx.x * kCols + threadIdx.x / kLanes;
+    const int lcol = threadIdx.x / kLanes;
+    const int col0 = blockIdx.x * kCols, col = col0 + lcol;
     const int h = blockIdx.y, seq = blockIdx.z;
     const int t0 = cu_q[seq], t1 = cu_q[seq + 1];
     if (t1 <= t0) return;
@@ -53,58 +67,76 @@ linear_recurrence_kernel(const float* __restrict__ q, const float* __restrict__ 
         const int c = lane + kLanes * i;
         S[i] = (c < d && !fresh) ? st[(int64_t)c * dv] : 0.f;
     }
-    float kk[PER], qq[PER], aa[PER], vv, bb = 1.f, a1 = 1.f;
-    auto fetch = [&](int t) {
-        const float* kr = k + t * qk_stride + (int64_t)g * d;
-        const float* qr = q + t * qk_stride + (int64_t)g * d;
-#pragma unroll
-        for (int i = 0; i < PER; ++i) {
-            const int c = lane + kLanes * i;
-            kk[i] = c < d ? kr[c] : 0.f;
-            qq[i] = c < d ? qr[c] : 0.f;
-            if (VECTOR_DECAY) aa[i] = c < d ? decay[t * decay_stride + (int64_t)h * d + c] : 1.f;
+    const int a_width = VECTOR_DECAY ? d : 1;
+    const int stage = kRecTile * (2 * d + a_width + kCols + 1);
+    // the operands of up to kRecTile tokens from ``tb`` on are asked for (asynchronous copies into buffer ``buf``)
+    auto stage_in = [&](int tb, int buf) {
+        float* qs = rec_smem + buf * stage;
+        float* ks = qs + kRecTile * d;
+        float* as = ks + kRecTile * d;
+        float* vs = as + kRecTile * a_width;
+        float* bs = vs + kRecTile * kCols;
+        const int nt = min(kRecTile, t1 - tb);
+        for (int i = threadIdx.x; i < nt * d; i += blockDim.x) {
+            const int tok = i / d, c = i % d;
+            cp_async_f32(qs + i, q + (int64_t)(tb + tok) * qk_stride + (int64_t)g * d + c);
+            cp_async_f32(ks + i, k + (int64_t)(tb + tok) * qk_stride + (int64_t)g * d + c);
+            if (VECTOR_DECAY) cp_async_f32(as + i, decay + (int64_t)(tb + tok) * decay_stride + (int64_t)h * d + c);
         }
-        if (!VECTOR_DECAY) a1 = decay[t * decay_stride + h];
-        vv = v[t * v_stride + (int64_t)h * dv + colc];
-        if (DELTA) bb = beta[t * beta_stride + h];
+        for (int i = threadIdx.x; i < nt * kCols; i += blockDim.x) {
+            const int tok = i / kCols, c = min(col0 + i % kCols, dv - 1);
+            cp_async_f32(vs + i, v + (int64_t)(tb + tok) * v_stride + (int64_t)h * dv + c);
+        }
+        if (threadIdx.x < nt) {
+            if (!VECTOR_DECAY) cp_async_f32(as + threadIdx.x, decay + (int64_t)(tb + threadIdx.x) * decay_stride + h);
+            if (DELTA) cp_async_f32(bs + threadIdx.x, beta + (int64_t)(tb + threadIdx.x) * beta_stride + h);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
     };
-    fetch(t0);
-    for (int t = t0; t < t1; ++t) {
-        float ck[PER], cq[PER], ca[PER];
-        const float cv = vv, cb = bb, c1 = a1;
-#pragma unroll
-        for (int i = 0; i < PER; ++i) {
-            ck[i] = kk[i];
-            cq[i] = qq[i];
-            ca[i] = VECTOR_DECAY ? aa[i] : c1;
-        }
-        if (t + 1 < t1) fetch(t + 1);              // the next token's operands are on their way while this one is worked
-        float u = cv;
-        if (DELTA) {
-            float dot = 0.f;
+    stage_in(t0, 0);
+    int buf = 0;
+    for (int tb = t0; tb < t1; tb += kRecTile, buf ^= 1) {
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncthreads();                                         // this tile has arrived; the other buffer is free again
+        if (tb + kRecTile < t1) stage_in(tb + kRecTile, buf ^ 1);
+        const float* qs = rec_smem + buf * stage;
+        const float* ks = qs + kRecTile * d;
+        const float* as = ks + kRecTile * d;
+        const float* vs = as + kRecTile * a_width;
+        const float* bs = vs + kRecTile * kCols;
+        const int nt = min(kRecTile, t1 - tb);
+        for (int tok = 0; tok < nt; ++tok) {
+            float ck[PER], cq[PER];
+            const float cv = vs[tok * kCols + lcol];
+            const float a1 = VECTOR_DECAY ? 1.f : as[tok];
 #pragma unroll
             for (int i = 0; i < PER; ++i) {
-                S[i] *= ca[i];
-                dot = fmaf(S[i], ck[i], dot);
+                const int c = lane + kLanes * i;
+                ck[i] = c < d ? ks[tok * d + c] : 0.f;
+                cq[i] = c < d ? qs[tok * d + c] : 0.f;
+                S[i] *= VECTOR_DECAY ? (c < d ? as[tok * d + c] : 1.f) : a1;
             }
-            dot += __shfl_xor_sync(0xffffffffu, dot, 1);
-            dot += __shfl_xor_sync(0xffffffffu, dot, 2);
-            dot += __shfl_xor_sync(0xffffffffu, dot, 4);
-            u = cb * (cv - dot);
-        } else {
+            float u = cv;
+            if (DELTA) {
+                float dot = 0.f;
 #pragma unroll
-            for (int i = 0; i < PER; ++i) S[i] *= ca[i];
-        }
-        float o = 0.f;
+                for (int i = 0; i < PER; ++i) dot = fmaf(S[i], ck[i], dot);
+                dot += __shfl_xor_sync(0xffffffffu, dot, 1);
+                dot += __shfl_xor_sync(0xffffffffu, dot, 2);
+                dot += __shfl_xor_sync(0xffffffffu, dot, 4);
+                u = bs[tok] * (cv - dot);
+            }
+            float o = 0.f;
 #pragma unroll
-        for (int i = 0; i < PER; ++i) {
-            S[i] = fmaf(ck[i], u, S[i]);
-            o = fmaf(S[i], cq[i], o);
+            for (int i = 0; i < PER; ++i) {
+                S[i] = fmaf(ck[i], u, S[i]);
+                o = fmaf(S[i], cq[i], o);
+            }
+            o += __shfl_xor_sync(0xffffffffu, o, 1);
+            o += __shfl_xor_sync(0xffffffffu, o, 2);
+            o += __shfl_xor_sync(0xffffffffu, o, 4);
+            if (lane == 0 && live) out[((int64_t)(tb + tok) * heads + h) * dv + col] = o * q_scale;
         }
-        o += __shfl_xor_sync(0xffffffffu, o, 1);
-        o += __shfl_xor_sync(0xffffffffu, o, 2);
-        o += __shfl_xor_sync(0xffffffffu, o, 4);
-        if (lane == 0 && live) out[((int64_t)t * heads + h) * dv + col] = o * q_scale;
     }
     if (live) {
 #pragma unroll
@@ -121,9 +153,13 @@ static void launch_recurrence(bool delta, bool vector_decay, dim3 grid, cudaStre
                               const float* beta, int64_t beta_stride, float* state, const int* positions, const int* cu_q,
                               const int* slots, float* out, int heads, int qk_heads, int d, int dv, float q_scale) {
     const dim3 block(kLanes * kCols);
-#define CPM_REC(D, V) cpm_launch(kLaunchAttention, linear_recurrence_kernel<PER, D, V>, grid, block, 0, stream, q, k, qk_stride, v, \
-                                 v_stride, decay, decay_stride, beta, beta_stride, state, positions, cu_q, slots, out, heads,      \
-                                 qk_heads, d, dv, q_scale)
+    const size_t smem = 2 * (size_t)recurrence_stage_floats(d, vector_decay) * sizeof(float);      // two buffers
+#define CPM_REC(D, V) do {                                                                                                         \
+        static bool configured[kMaxDevices] = {};                                                                                  \
+        if (smem > 48 * 1024 && ensure_dynamic_smem(linear_recurrence_kernel<PER, D, V>, 100 * 1024, configured) != CPM_OK) return; \
+        cpm_launch(kLaunchAttention, linear_recurrence_kernel<PER, D, V>, grid, block, smem, stream, q, k, qk_stride, v, v_stride,   \
+                   decay, decay_stride, beta, beta_stride, state, positions, cu_q, slots, out, heads, qk_heads, d, dv, q_scale);   \
+    } while (0)
     if (delta && vector_decay) CPM_REC(true, true);
     else if (delta) CPM_REC(true, false);
     else if (vector_decay) CPM_REC(false, true);

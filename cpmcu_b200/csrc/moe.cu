@@ -208,6 +208,121 @@ moe_tile_kernel(const T* __restrict__ A, const T* __restrict__ B0, const T* __re
     }
 }
 
+
+// The same products for bf16 on the tensor cores (mma.sync m16n8k16, fp32 accumulation): tiles of 64 places of one
+// expert times 64 output features, four warps of 16 rows each, K in steps of 32 through shared memory (rows padded to
+// 40 elements: the fragments' 32-bit loads then hit 32 different banks), the next step's global loads issued before
+// the current step's products.  K must be a multiple of 8 (16-byte loads).
+constexpr int kMmaM = 64, kMmaN = 64, kMmaK = 32, kMmaPad = 40;
+
+__device__ __forceinline__ void mma_bf16_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+template <bool GATED>
+__global__ void __launch_bounds__(128)
+moe_tile_mma_kernel(const bf16* __restrict__ A, const bf16* __restrict__ B0, const bf16* __restrict__ B1, bf16* __restrict__ C,
+                    const int* __restrict__ offsets, const int* __restrict__ order, int E, int top, int N, int K) {
+    __shared__ __align__(16) bf16 As[kMmaM][kMmaPad], Bs0[kMmaN][kMmaPad], Bs1[GATED ? kMmaN : 1][kMmaPad];
+    __shared__ int s_tile[3];
+    __shared__ int s_rows[kMmaM];
+    pdl_launch_dependents();
+    pdl_wait();
+    if (threadIdx.x == 0) {
+        int tile = blockIdx.x, e = 0, found = -1, first = 0;
+        for (; e < E; ++e) {
+            const int n = offsets[e + 1] - offsets[e];
+            const int tiles = (n + kMmaM - 1) / kMmaM;
+            if (tile < tiles) { found = e; first = offsets[e] + tile * kMmaM; break; }
+            tile -= tiles;
+        }
+        s_tile[0] = found;
+        s_tile[1] = first;
+        s_tile[2] = found >= 0 ? min(kMmaM, offsets[found + 1] - first) : 0;
+    }
+    __syncthreads();
+    const int e = s_tile[0], r0 = s_tile[1], rows = s_tile[2];
+    if (e < 0) return;
+    if (threadIdx.x < kMmaM) {
+        const int r = threadIdx.x;
+        s_rows[r] = r < rows ? order[r0 + r] : -1;          // the pair at this place
+    }
+    __syncthreads();
+    const int n0 = blockIdx.y * kMmaN;
+    const bf16* W0 = B0 + (int64_t)e * N * K;
+    const bf16* W1 = GATED ? B1 + (int64_t)e * N * K : nullptr;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, j = lane & 3;
+    // a thread's two 16-byte pieces of each tile: piece p covers row (p >> 2), elements 8 * (p & 3) ..
+    uint4 ra[2], rb0[2], rb1[2];
+    auto fetch = [&](int k0) {
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const int p = threadIdx.x + 128 * i, r = p >> 2, kk = k0 + 8 * (p & 3);
+            ra[i] = rb0[i] = rb1[i] = make_uint4(0, 0, 0, 0);
+            if (kk < K) {
+                const int pair = s_rows[r];
+                if (pair >= 0) ra[i] = *reinterpret_cast<const uint4*>(A + (int64_t)(GATED ? pair / top : r0 + r) * K + kk);
+                if (n0 + r < N) {
+                    rb0[i] = *reinterpret_cast<const uint4*>(W0 + (int64_t)(n0 + r) * K + kk);
+                    if (GATED) rb1[i] = *reinterpret_cast<const uint4*>(W1 + (int64_t)(n0 + r) * K + kk);
+                }
+            }
+        }
+    };
+    float acc0[8][4] = {}, acc1[GATED ? 8 : 1][4] = {};
+    fetch(0);
+    for (int k0 = 0; k0 < K; k0 += kMmaK) {
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const int p = threadIdx.x + 128 * i, r = p >> 2, c = 8 * (p & 3);
+            *reinterpret_cast<uint4*>(&As[r][c]) = ra[i];
+            *reinterpret_cast<uint4*>(&Bs0[r][c]) = rb0[i];
+            if (GATED) *reinterpret_cast<uint4*>(&Bs1[r][c]) = rb1[i];
+        }
+        __syncthreads();
+        if (k0 + kMmaK < K) fetch(k0 + kMmaK);
+#pragma unroll
+        for (int ks = 0; ks < kMmaK; ks += 16) {
+            uint32_t a[4];
+            a[0] = *reinterpret_cast<const uint32_t*>(&As[warp * 16 + g][ks + 2 * j]);
+            a[1] = *reinterpret_cast<const uint32_t*>(&As[warp * 16 + g + 8][ks + 2 * j]);
+            a[2] = *reinterpret_cast<const uint32_t*>(&As[warp * 16 + g][ks + 2 * j + 8]);
+            a[3] = *reinterpret_cast<const uint32_t*>(&As[warp * 16 + g + 8][ks + 2 * j + 8]);
+#pragma unroll
+            for (int nt = 0; nt < 8; ++nt) {
+                const uint32_t b0 = *reinterpret_cast<const uint32_t*>(&Bs0[nt * 8 + g][ks + 2 * j]);
+                const uint32_t b1 = *reinterpret_cast<const uint32_t*>(&Bs0[nt * 8 + g][ks + 2 * j + 8]);
+                mma_bf16_16816(acc0[nt], a, b0, b1);
+                if (GATED) {
+                    const uint32_t u0 = *reinterpret_cast<const uint32_t*>(&Bs1[nt * 8 + g][ks + 2 * j]);
+                    const uint32_t u1 = *reinterpret_cast<const uint32_t*>(&Bs1[nt * 8 + g][ks + 2 * j + 8]);
+                    mma_bf16_16816(acc1[nt], a, u0, u1);
+                }
+            }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+        const int r = warp * 16 + g + 8 * half;
+        if (r >= rows) continue;
+        const int64_t dst = GATED ? (int64_t)(r0 + r) : (int64_t)s_rows[r];
+#pragma unroll
+        for (int nt = 0; nt < 8; ++nt) {
+#pragma unroll
+            for (int q = 0; q < 2; ++q) {
+                const int n = n0 + nt * 8 + 2 * j + q;
+                if (n >= N) continue;
+                float v = acc0[nt][2 * half + q];
+                if (GATED) v = v / (1.0f + expf(-v)) * acc1[nt][2 * half + q];
+                C[dst * N + n] = __float2bfloat16_rn(v);
+            }
+        }
+    }
+}
+
 // out[t] = sum_k weights[t][k] * Y[t * top + k] + gate[t] * shared[t]
 template <typename T>
 __global__ void moe_combine_kernel(const T* __restrict__ Y, const float* __restrict__ weights, const T* __restrict__ shared,
@@ -221,6 +336,13 @@ __global__ void moe_combine_kernel(const T* __restrict__ Y, const float* __restr
         if (shared) v = fmaf(gate ? gate[t] : 1.f, to_f32(shared[t * W + c]), v);
         out[t * W + c] = from_f32<T>(v);
     }
+}
+
+static int g_moe_tensor_cores = 1;
+// 0: the bf16 products stay on the CUDA cores too (for comparisons and tests)
+CPM_API int cpm_set_moe_tensor_cores(int on) {
+    g_moe_tensor_cores = on;
+    return CPM_OK;
 }
 
 CPM_API int cpm_moe_route(const float* logits, int ld, const float* correction, int* chosen, float* weights, float* shared_gate,
@@ -250,6 +372,18 @@ CPM_API int cpm_moe_expert_product(const void* A, const void* B0, const void* B1
                                    int n_pairs, int E, int top, int N, int K, int gated, int dtype, cudaStream_t stream) {
     if (n_pairs <= 0) return CPM_OK;
     if (E < 1 || top < 1 || N < 1 || K < 1) return CPM_BAD_ARGUMENT;
+    if (dtype == CPM_BF16 && K % 8 == 0 && ((uintptr_t)A & 15) == 0 && ((uintptr_t)B0 & 15) == 0 && ((uintptr_t)B1 & 15) == 0 &&
+        g_moe_tensor_cores) {
+        const dim3 mgrid((n_pairs + kMmaM - 1) / kMmaM + E, (N + kMmaN - 1) / kMmaN);
+        if (mgrid.y > 65535) return CPM_BAD_ARGUMENT;
+        if (gated)
+            cpm_launch(kLaunchProduct, moe_tile_mma_kernel<true>, mgrid, dim3(128), 0, stream, (const bf16*)A, (const bf16*)B0,
+                       (const bf16*)B1, (bf16*)C, offsets, order, E, top, N, K);
+        else
+            cpm_launch(kLaunchProduct, moe_tile_mma_kernel<false>, mgrid, dim3(128), 0, stream, (const bf16*)A, (const bf16*)B0,
+                       (const bf16*)B1, (bf16*)C, offsets, order, E, top, N, K);
+        return launch_status();
+    }
     const dim3 grid((n_pairs + kTileM - 1) / kTileM + E, (N + kTileN - 1) / kTileN);
     if (grid.y > 65535) return CPM_BAD_ARGUMENT;
 #define CPM_MOE(TT, G) cpm_launch(kLaunchProduct, moe_tile_kernel<TT, G>, grid, dim3(256), 0, stream, (const TT*)A, (const TT*)B0, \
