@@ -24,8 +24,7 @@ __device__ __forceinline__ float silu_acc(float v) { return v / (1.0f + expf(-v)
 // log(1 + e^v) without overflow
 __device__ __forceinline__ float softplus_acc(float v) { return fmaxf(v, 0.f) + log1pf(expf(-fabsf(v))); }
 
-constexpr int kLanes = 8;      // threads that share one value column
-constexpr int kCols = 32;      // value columns per block
+constexpr int kRecThreads = 256;
 constexpr int kRecTile = 8;    // tokens whose operands are staged in shared memory at a time
 
 __device__ __forceinline__ void cp_async_f32(float* smem_dst, const float* gmem_src) {
@@ -33,13 +32,22 @@ __device__ __forceinline__ void cp_async_f32(float* smem_dst, const float* gmem_
     asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" :: "r"(dst), "l"(gmem_src) : "memory");
 }
 
-// Floats of one staging buffer: q and k [tile][d], the decay [tile][d] or [tile], v [tile][kCols], beta [tile].
-static inline int recurrence_stage_floats(int d, bool vector_decay) {
-    return kRecTile * (2 * d + (vector_decay ? d : 1) + kCols + 1);
+// Floats of one staging buffer: q and k [tile][d], the decay [tile][d] or [tile], v [tile][columns], beta [tile].
+static inline int recurrence_stage_floats(int d, bool vector_decay, int cols) {
+    return kRecTile * (2 * d + (vector_decay ? d : 1) + cols + 1);
 }
 
-template <int PER, bool DELTA, bool VECTOR_DECAY>
-__global__ void __launch_bounds__(kLanes * kCols)
+template <int W>
+__device__ __forceinline__ float lanes_sum(float v) {      // over the W consecutive threads of a column
+#pragma unroll
+    for (int o = 1; o < W; o <<= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+// kLanes threads share a column (8 for key sizes up to 64, 16 above: shorter chains of dependent products per token);
+// a block of 256 threads holds 256 / kLanes columns; PER key channels a thread.
+template <int kLanes, int PER, bool DELTA, bool VECTOR_DECAY>
+__global__ void __launch_bounds__(kRecThreads)
 linear_recurrence_kernel(const float* __restrict__ q, const float* __restrict__ k, int64_t qk_stride,      // [tokens, qk_heads, d]
                          const float* __restrict__ v, int64_t v_stride,                                    // [tokens, heads, dv]
                          const float* __restrict__ decay, int64_t decay_stride,                            // [tokens, heads(, d)]
@@ -48,6 +56,8 @@ linear_recurrence_kernel(const float* __restrict__ q, const float* __restrict__ 
                          const int* __restrict__ slots, float* __restrict__ out,                           // [tokens, heads, dv]
                          int heads, int qk_heads, int d, int dv, float q_scale) {
     extern __shared__ float rec_smem[];
+    constexpr int kCols = kRecThreads / kLanes;
+    constexpr int kAcc = PER >= 8 ? 8 : 4;
     pdl_launch_dependents();
     pdl_wait();
     const int lane = threadIdx.x % kLanes;
@@ -118,23 +128,26 @@ linear_recurrence_kernel(const float* __restrict__ q, const float* __restrict__ 
             }
             float u = cv;
             if (DELTA) {
-                float dot = 0.f;
+                float dot[kAcc] = {};                          // partial sums: short chains of dependent products
 #pragma unroll
-                for (int i = 0; i < PER; ++i) dot = fmaf(S[i], ck[i], dot);
-                dot += __shfl_xor_sync(0xffffffffu, dot, 1);
-                dot += __shfl_xor_sync(0xffffffffu, dot, 2);
-                dot += __shfl_xor_sync(0xffffffffu, dot, 4);
-                u = bs[tok] * (cv - dot);
+                for (int i = 0; i < PER; ++i) dot[i % kAcc] = fmaf(S[i], ck[i], dot[i % kAcc]);
+#pragma unroll
+                for (int w = kAcc / 2; w > 0; w >>= 1)
+#pragma unroll
+                    for (int i = 0; i < w; ++i) dot[i] += dot[i + w];
+                u = bs[tok] * (cv - lanes_sum<kLanes>(dot[0]));
             }
-            float o = 0.f;
+            float op[kAcc] = {};
 #pragma unroll
             for (int i = 0; i < PER; ++i) {
                 S[i] = fmaf(ck[i], u, S[i]);
-                o = fmaf(S[i], cq[i], o);
+                op[i % kAcc] = fmaf(S[i], cq[i], op[i % kAcc]);
             }
-            o += __shfl_xor_sync(0xffffffffu, o, 1);
-            o += __shfl_xor_sync(0xffffffffu, o, 2);
-            o += __shfl_xor_sync(0xffffffffu, o, 4);
+#pragma unroll
+            for (int w = kAcc / 2; w > 0; w >>= 1)
+#pragma unroll
+                for (int i = 0; i < w; ++i) op[i] += op[i + w];
+            const float o = lanes_sum<kLanes>(op[0]);
             if (lane == 0 && live) out[((int64_t)(tb + tok) * heads + h) * dv + col] = o * q_scale;
         }
     }
@@ -147,24 +160,35 @@ linear_recurrence_kernel(const float* __restrict__ q, const float* __restrict__ 
     }
 }
 
-template <int PER>
-static void launch_recurrence(bool delta, bool vector_decay, dim3 grid, cudaStream_t stream, const float* q, const float* k,
+template <int LANES, int PER>
+static void launch_recurrence(bool delta, bool vector_decay, cudaStream_t stream, const float* q, const float* k,
                               int64_t qk_stride, const float* v, int64_t v_stride, const float* decay, int64_t decay_stride,
                               const float* beta, int64_t beta_stride, float* state, const int* positions, const int* cu_q,
-                              const int* slots, float* out, int heads, int qk_heads, int d, int dv, float q_scale) {
-    const dim3 block(kLanes * kCols);
-    const size_t smem = 2 * (size_t)recurrence_stage_floats(d, vector_decay) * sizeof(float);      // two buffers
-#define CPM_REC(D, V) do {                                                                                                         \
-        static bool configured[kMaxDevices] = {};                                                                                  \
-        if (smem > 48 * 1024 && ensure_dynamic_smem(linear_recurrence_kernel<PER, D, V>, 100 * 1024, configured) != CPM_OK) return; \
-        cpm_launch(kLaunchAttention, linear_recurrence_kernel<PER, D, V>, grid, block, smem, stream, q, k, qk_stride, v, v_stride,   \
-                   decay, decay_stride, beta, beta_stride, state, positions, cu_q, slots, out, heads, qk_heads, d, dv, q_scale);   \
+                              const int* slots, float* out, int n_seqs, int heads, int qk_heads, int d, int dv, float q_scale) {
+    constexpr int cols = kRecThreads / LANES;
+    const dim3 grid((dv + cols - 1) / cols, heads, n_seqs), block(kRecThreads);
+    const size_t smem = 2 * (size_t)recurrence_stage_floats(d, vector_decay, cols) * sizeof(float);      // two buffers
+#define CPM_REC(D, V) do {                                                                                                          \
+        static bool configured[kMaxDevices] = {};                                                                                   \
+        if (smem > 48 * 1024 && ensure_dynamic_smem(linear_recurrence_kernel<LANES, PER, D, V>, 100 * 1024, configured) != CPM_OK)  \
+            return;                                                                                                                 \
+        cpm_launch(kLaunchAttention, linear_recurrence_kernel<LANES, PER, D, V>, grid, block, smem, stream, q, k, qk_stride, v,     \
+                   v_stride, decay, decay_stride, beta, beta_stride, state, positions, cu_q, slots, out, heads, qk_heads, d, dv,    \
+                   q_scale);                                                                                                        \
     } while (0)
     if (delta && vector_decay) CPM_REC(true, true);
     else if (delta) CPM_REC(true, false);
     else if (vector_decay) CPM_REC(false, true);
     else CPM_REC(false, false);
 #undef CPM_REC
+}
+
+static int g_recurrence_lanes = 8;
+// How many threads share a value column: 8 up to a key size of 64 and 16 above (the default), or, when set to 4, four
+// (measured slower at 2,048 tokens: 1,285 against 783 us for 16 heads of 128 x 128).
+CPM_API int cpm_set_recurrence_lanes(int lanes) {
+    g_recurrence_lanes = lanes;
+    return CPM_OK;
 }
 
 // q, k: fp32 rows of ``qk_stride`` floats holding [qk_heads, d]; v: rows of ``v_stride`` floats holding [heads, dv];
@@ -176,16 +200,23 @@ CPM_API int cpm_linear_recurrence(const float* q, const float* k, int64_t qk_str
                                   float* out, int n_seqs, int heads, int qk_heads, int d, int dv, float q_scale,
                                   cudaStream_t stream) {
     if (n_seqs <= 0) return CPM_OK;
-    if (heads < 1 || qk_heads < 1 || heads % qk_heads || d < 1 || dv < 1 || d > kLanes * 32) return CPM_BAD_ARGUMENT;
-    const dim3 grid((dv + kCols - 1) / kCols, heads, n_seqs);
+    if (heads < 1 || qk_heads < 1 || heads % qk_heads || d < 1 || dv < 1 || d > 256) return CPM_BAD_ARGUMENT;
     const bool delta = beta != nullptr;
-#define CPM_REC_PER(P) launch_recurrence<P>(delta, vector_decay != 0, grid, stream, q, k, qk_stride, v, v_stride, decay, decay_stride, \
-                                            beta, beta_stride, state, positions, cu_q, slots, out, heads, qk_heads, d, dv, q_scale)
-    const int per = (d + kLanes - 1) / kLanes;
-    if (per <= 4) CPM_REC_PER(4);
-    else if (per <= 8) CPM_REC_PER(8);
-    else if (per <= 16) CPM_REC_PER(16);
-    else CPM_REC_PER(32);
+#define CPM_REC_PER(L, P) launch_recurrence<L, P>(delta, vector_decay != 0, stream, q, k, qk_stride, v, v_stride, decay, decay_stride, \
+                                                  beta, beta_stride, state, positions, cu_q, slots, out, n_seqs, heads, qk_heads, d,  \
+                                                  dv, q_scale)
+    const int lanes = g_recurrence_lanes;
+    if (lanes == 4) {
+        if (d <= 32) CPM_REC_PER(4, 8);
+        else if (d <= 64) CPM_REC_PER(4, 16);
+        else if (d <= 128) CPM_REC_PER(4, 32);
+        else CPM_REC_PER(8, 32);
+    } else {
+        if (d <= 32) CPM_REC_PER(8, 4);
+        else if (d <= 64) CPM_REC_PER(8, 8);
+        else if (d <= 128) CPM_REC_PER(16, 8);
+        else CPM_REC_PER(16, 16);
+    }
 #undef CPM_REC_PER
     return launch_status();
 }

@@ -11,7 +11,7 @@
 //   gated:  H[r] = silu(x[token(r)] Wg_e^T) * (x[token(r)] Wu_e^T)     r: place in expert order
 //   down:   Y[pair(r)] = H[r] Wd_e^T
 // and a last kernel adds up a token's pairs with their weights and the shared expert's output times its gate.
-// Accumulation is fp32 on the CUDA cores for both storage types.
+// Accumulation is fp32: on the CUDA cores for 32-bit storage (and where K is no multiple of 8), on the tensor cores for bf16.
 #include "common.cuh"
 
 constexpr int kRouteMaxPerLane = 16;      // experts <= 512
@@ -209,11 +209,11 @@ moe_tile_kernel(const T* __restrict__ A, const T* __restrict__ B0, const T* __re
 }
 
 
-// The same products for bf16 on the tensor cores (mma.sync m16n8k16, fp32 accumulation): tiles of 64 places of one
-// expert times 64 output features, four warps of 16 rows each, K in steps of 32 through shared memory (rows padded to
-// 40 elements: the fragments' 32-bit loads then hit 32 different banks), the next step's global loads issued before
-// the current step's products.  K must be a multiple of 8 (16-byte loads).
-constexpr int kMmaM = 64, kMmaN = 64, kMmaK = 32, kMmaPad = 40;
+// The same products for bf16 on the tensor cores (mma.sync m16n8k16, fp32 accumulation): tiles of 128 places of one
+// expert times 64 output features, eight warps of 32 x 32 each, K in steps of 32 through two shared-memory stages
+// filled by asynchronous 16-byte copies (rows padded to 40 elements, so that ldmatrix reads 8 rows from 8 different
+// bank groups); fragments come by ldmatrix.x4.  K must be a multiple of 8 (16-byte copies).
+constexpr int kMmaM = 128, kMmaN = 64, kMmaK = 32, kMmaPad = 40;
 
 __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
@@ -221,11 +221,24 @@ __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], const uint32_t (&a
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const bf16* smem_row) {
+    const uint32_t addr = (uint32_t)__cvta_generic_to_shared(smem_row);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+
+// 16 bytes from global to shared memory, or 16 zero bytes when ``valid`` is false (the source is then not read)
+__device__ __forceinline__ void cp_async_16(bf16* smem_dst, const bf16* gmem_src, bool valid) {
+    const uint32_t dst = (uint32_t)__cvta_generic_to_shared(smem_dst);
+    const int bytes = valid ? 16 : 0;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" :: "r"(dst), "l"(gmem_src), "r"(bytes) : "memory");
+}
+
 template <bool GATED>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(256)
 moe_tile_mma_kernel(const bf16* __restrict__ A, const bf16* __restrict__ B0, const bf16* __restrict__ B1, bf16* __restrict__ C,
                     const int* __restrict__ offsets, const int* __restrict__ order, int E, int top, int N, int K) {
-    __shared__ __align__(16) bf16 As[kMmaM][kMmaPad], Bs0[kMmaN][kMmaPad], Bs1[GATED ? kMmaN : 1][kMmaPad];
+    __shared__ __align__(16) bf16 As[2][kMmaM][kMmaPad], Bs0[2][kMmaN][kMmaPad], Bs1[GATED ? 2 : 1][GATED ? kMmaN : 1][kMmaPad];
     __shared__ int s_tile[3];
     __shared__ int s_rows[kMmaM];
     pdl_launch_dependents();
@@ -245,82 +258,81 @@ moe_tile_mma_kernel(const bf16* __restrict__ A, const bf16* __restrict__ B0, con
     __syncthreads();
     const int e = s_tile[0], r0 = s_tile[1], rows = s_tile[2];
     if (e < 0) return;
-    if (threadIdx.x < kMmaM) {
-        const int r = threadIdx.x;
-        s_rows[r] = r < rows ? order[r0 + r] : -1;          // the pair at this place
-    }
+    if (threadIdx.x < kMmaM) s_rows[threadIdx.x] = threadIdx.x < rows ? order[r0 + threadIdx.x] : -1;      // the pair at this place
     __syncthreads();
     const int n0 = blockIdx.y * kMmaN;
     const bf16* W0 = B0 + (int64_t)e * N * K;
-    const bf16* W1 = GATED ? B1 + (int64_t)e * N * K : nullptr;
+    const bf16* W1 = GATED ? B1 + (int64_t)e * N * K : B0;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, j = lane & 3;
-    // a thread's two 16-byte pieces of each tile: piece p covers row (p >> 2), elements 8 * (p & 3) ..
-    uint4 ra[2], rb0[2], rb1[2];
-    auto fetch = [&](int k0) {
+    const int wm = warp >> 1, wn = warp & 1;                   // the warp's 32 rows and 32 columns of the tile
+    // a thread's source rows: two pieces of the A tile (rows p >> 2 for p = tid, tid + 256), one of each B tile
+    const bf16* a_src[2];
+    bool a_ok[2];
 #pragma unroll
-        for (int i = 0; i < 2; ++i) {
-            const int p = threadIdx.x + 128 * i, r = p >> 2, kk = k0 + 8 * (p & 3);
-            ra[i] = rb0[i] = rb1[i] = make_uint4(0, 0, 0, 0);
-            if (kk < K) {
-                const int pair = s_rows[r];
-                if (pair >= 0) ra[i] = *reinterpret_cast<const uint4*>(A + (int64_t)(GATED ? pair / top : r0 + r) * K + kk);
-                if (n0 + r < N) {
-                    rb0[i] = *reinterpret_cast<const uint4*>(W0 + (int64_t)(n0 + r) * K + kk);
-                    if (GATED) rb1[i] = *reinterpret_cast<const uint4*>(W1 + (int64_t)(n0 + r) * K + kk);
-                }
-            }
-        }
+    for (int i = 0; i < 2; ++i) {
+        const int r = (threadIdx.x + 256 * i) >> 2;
+        const int pair = s_rows[r];
+        a_ok[i] = pair >= 0;
+        a_src[i] = A + (int64_t)(a_ok[i] ? (GATED ? pair / top : r0 + r) : 0) * K;
+    }
+    const int b_row = threadIdx.x >> 2, piece = 8 * (threadIdx.x & 3);
+    const bool b_ok = n0 + b_row < N;
+    const bf16* b_src0 = W0 + (int64_t)(b_ok ? n0 + b_row : 0) * K;
+    const bf16* b_src1 = W1 + (int64_t)(b_ok ? n0 + b_row : 0) * K;
+    auto issue = [&](int k0, int st) {
+        const bool k_ok = k0 + piece < K;
+#pragma unroll
+        for (int i = 0; i < 2; ++i)
+            cp_async_16(&As[st][(threadIdx.x + 256 * i) >> 2][piece], a_src[i] + (k_ok ? k0 + piece : 0), a_ok[i] && k_ok);
+        cp_async_16(&Bs0[st][b_row][piece], b_src0 + (k_ok ? k0 + piece : 0), b_ok && k_ok);
+        if (GATED) cp_async_16(&Bs1[st][b_row][piece], b_src1 + (k_ok ? k0 + piece : 0), b_ok && k_ok);
+        asm volatile("cp.async.commit_group;" ::: "memory");
     };
-    float acc0[8][4] = {}, acc1[GATED ? 8 : 1][4] = {};
-    fetch(0);
-    for (int k0 = 0; k0 < K; k0 += kMmaK) {
-#pragma unroll
-        for (int i = 0; i < 2; ++i) {
-            const int p = threadIdx.x + 128 * i, r = p >> 2, c = 8 * (p & 3);
-            *reinterpret_cast<uint4*>(&As[r][c]) = ra[i];
-            *reinterpret_cast<uint4*>(&Bs0[r][c]) = rb0[i];
-            if (GATED) *reinterpret_cast<uint4*>(&Bs1[r][c]) = rb1[i];
-        }
-        __syncthreads();
-        if (k0 + kMmaK < K) fetch(k0 + kMmaK);
+    float acc0[2][4][4] = {}, acc1[GATED ? 2 : 1][4][4] = {};
+    issue(0, 0);
+    int st = 0;
+    for (int k0 = 0; k0 < K; k0 += kMmaK, st ^= 1) {
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncthreads();                                       // this stage has arrived; the other one is free again
+        if (k0 + kMmaK < K) issue(k0 + kMmaK, st ^ 1);
 #pragma unroll
         for (int ks = 0; ks < kMmaK; ks += 16) {
-            uint32_t a[4];
-            a[0] = *reinterpret_cast<const uint32_t*>(&As[warp * 16 + g][ks + 2 * j]);
-            a[1] = *reinterpret_cast<const uint32_t*>(&As[warp * 16 + g + 8][ks + 2 * j]);
-            a[2] = *reinterpret_cast<const uint32_t*>(&As[warp * 16 + g][ks + 2 * j + 8]);
-            a[3] = *reinterpret_cast<const uint32_t*>(&As[warp * 16 + g + 8][ks + 2 * j + 8]);
+            uint32_t a[2][4], b[2][4], u[2][4];
 #pragma unroll
-            for (int nt = 0; nt < 8; ++nt) {
-                const uint32_t b0 = *reinterpret_cast<const uint32_t*>(&Bs0[nt * 8 + g][ks + 2 * j]);
-                const uint32_t b1 = *reinterpret_cast<const uint32_t*>(&Bs0[nt * 8 + g][ks + 2 * j + 8]);
-                mma_bf16_16816(acc0[nt], a, b0, b1);
-                if (GATED) {
-                    const uint32_t u0 = *reinterpret_cast<const uint32_t*>(&Bs1[nt * 8 + g][ks + 2 * j]);
-                    const uint32_t u1 = *reinterpret_cast<const uint32_t*>(&Bs1[nt * 8 + g][ks + 2 * j + 8]);
-                    mma_bf16_16816(acc1[nt], a, u0, u1);
+            for (int mt = 0; mt < 2; ++mt) ldmatrix_x4(a[mt], &As[st][wm * 32 + mt * 16 + (lane & 15)][ks + 8 * (lane >> 4)]);
+#pragma unroll
+            for (int np = 0; np < 2; ++np) {                   // two column tiles of 8 per ldmatrix
+                const int row = wn * 32 + np * 16 + 8 * (lane >> 4) + (lane & 7), col = ks + 8 * ((lane >> 3) & 1);
+                ldmatrix_x4(b[np], &Bs0[st][row][col]);
+                if (GATED) ldmatrix_x4(u[np], &Bs1[st][row][col]);
+            }
+#pragma unroll
+            for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+                for (int nt = 0; nt < 4; ++nt) {
+                    mma_bf16_16816(acc0[mt][nt], a[mt], b[nt >> 1][2 * (nt & 1)], b[nt >> 1][2 * (nt & 1) + 1]);
+                    if (GATED) mma_bf16_16816(acc1[mt][nt], a[mt], u[nt >> 1][2 * (nt & 1)], u[nt >> 1][2 * (nt & 1) + 1]);
                 }
-            }
-        }
-        __syncthreads();
-    }
-#pragma unroll
-    for (int half = 0; half < 2; ++half) {
-        const int r = warp * 16 + g + 8 * half;
-        if (r >= rows) continue;
-        const int64_t dst = GATED ? (int64_t)(r0 + r) : (int64_t)s_rows[r];
-#pragma unroll
-        for (int nt = 0; nt < 8; ++nt) {
-#pragma unroll
-            for (int q = 0; q < 2; ++q) {
-                const int n = n0 + nt * 8 + 2 * j + q;
-                if (n >= N) continue;
-                float v = acc0[nt][2 * half + q];
-                if (GATED) v = v / (1.0f + expf(-v)) * acc1[nt][2 * half + q];
-                C[dst * N + n] = __float2bfloat16_rn(v);
-            }
         }
     }
+#pragma unroll
+    for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            const int r = wm * 32 + mt * 16 + g + 8 * half;
+            if (r >= rows) continue;
+            const int64_t dst = GATED ? (int64_t)(r0 + r) : (int64_t)s_rows[r];
+#pragma unroll
+            for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+                for (int q = 0; q < 2; ++q) {
+                    const int n = n0 + wn * 32 + nt * 8 + 2 * j + q;
+                    if (n >= N) continue;
+                    float v = acc0[mt][nt][2 * half + q];
+                    if (GATED) v = v / (1.0f + expf(-v)) * acc1[mt][nt][2 * half + q];
+                    C[dst * N + n] = __float2bfloat16_rn(v);
+                }
+        }
 }
 
 // out[t] = sum_k weights[t][k] * Y[t * top + k] + gate[t] * shared[t]
@@ -377,10 +389,10 @@ CPM_API int cpm_moe_expert_product(const void* A, const void* B0, const void* B1
         const dim3 mgrid((n_pairs + kMmaM - 1) / kMmaM + E, (N + kMmaN - 1) / kMmaN);
         if (mgrid.y > 65535) return CPM_BAD_ARGUMENT;
         if (gated)
-            cpm_launch(kLaunchProduct, moe_tile_mma_kernel<true>, mgrid, dim3(128), 0, stream, (const bf16*)A, (const bf16*)B0,
+            cpm_launch(kLaunchProduct, moe_tile_mma_kernel<true>, mgrid, dim3(256), 0, stream, (const bf16*)A, (const bf16*)B0,
                        (const bf16*)B1, (bf16*)C, offsets, order, E, top, N, K);
         else
-            cpm_launch(kLaunchProduct, moe_tile_mma_kernel<false>, mgrid, dim3(128), 0, stream, (const bf16*)A, (const bf16*)B0,
+            cpm_launch(kLaunchProduct, moe_tile_mma_kernel<false>, mgrid, dim3(256), 0, stream, (const bf16*)A, (const bf16*)B0,
                        (const bf16*)B1, (bf16*)C, offsets, order, E, top, N, K);
         return launch_status();
     }
