@@ -335,6 +335,75 @@ moe_tile_mma_kernel(const bf16* __restrict__ A, const bf16* __restrict__ B0, con
         }
 }
 
+// Few pairs (a decode step): every pair is a matrix-vector product that streams its expert's weights once.  A block
+// takes one pair and 32 output features (64 weight rows when gated), a warp four of them at a time: the lanes split K
+// in 16-byte pieces and the sums meet by shuffles.  No grouping by expert is needed: H and Y are indexed by pair.
+constexpr int kGemvFeatures = 32;
+
+template <bool GATED>
+__global__ void __launch_bounds__(256)
+moe_pair_gemv_kernel(const bf16* __restrict__ A, const bf16* __restrict__ B0, const bf16* __restrict__ B1, bf16* __restrict__ C,
+                     const int* __restrict__ chosen, int top, int N, int K) {
+    extern __shared__ float gemv_x[];                          // the pair's input row, fp32
+    pdl_launch_dependents();
+    const int pair = blockIdx.x, n0 = blockIdx.y * kGemvFeatures;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    pdl_wait();
+    const int e = chosen[pair];
+    const bf16* x = A + (int64_t)(GATED ? pair / top : pair) * K;
+    for (int i = threadIdx.x; i < K; i += blockDim.x) gemv_x[i] = __bfloat162float(x[i]);
+    __syncthreads();
+    const bf16* W0 = B0 + (int64_t)e * N * K;
+    const bf16* W1 = GATED ? B1 + (int64_t)e * N * K : B0;
+    for (int f = warp; f < kGemvFeatures; f += 8) {
+        const int n = n0 + f;
+        if (n >= N) break;
+        const bf16* w0 = W0 + (int64_t)n * K;
+        const bf16* w1 = W1 + (int64_t)n * K;
+        float s0 = 0.f, s1 = 0.f;
+        for (int kk = lane * 8; kk < K; kk += 256) {
+            const uint4 r0 = *reinterpret_cast<const uint4*>(w0 + kk);
+            const __nv_bfloat162* p0 = reinterpret_cast<const __nv_bfloat162*>(&r0);
+            uint4 r1 = make_uint4(0, 0, 0, 0);
+            if (GATED) r1 = *reinterpret_cast<const uint4*>(w1 + kk);
+            const __nv_bfloat162* p1 = reinterpret_cast<const __nv_bfloat162*>(&r1);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float2 a = __bfloat1622float2(p0[i]);
+                s0 = fmaf(a.x, gemv_x[kk + 2 * i], s0);
+                s0 = fmaf(a.y, gemv_x[kk + 2 * i + 1], s0);
+                if (GATED) {
+                    const float2 b = __bfloat1622float2(p1[i]);
+                    s1 = fmaf(b.x, gemv_x[kk + 2 * i], s1);
+                    s1 = fmaf(b.y, gemv_x[kk + 2 * i + 1], s1);
+                }
+            }
+        }
+        s0 = warp_sum(s0);
+        if (GATED) s1 = warp_sum(s1);
+        if (lane == 0) C[(int64_t)pair * N + n] = __float2bfloat16_rn(GATED ? s0 / (1.0f + expf(-s0)) * s1 : s0);
+    }
+}
+
+// The same two products for few pairs, by pair: gated: C = H [pairs, N] by pair from x [tokens, K]; else C = Y [pairs, N]
+// from H [pairs, K] by pair.  bf16, K a multiple of 8.
+CPM_API int cpm_moe_pair_product(const void* A, const void* B0, const void* B1, void* C, const int* chosen, int n_pairs, int top,
+                                 int N, int K, int gated, cudaStream_t stream) {
+    if (n_pairs <= 0) return CPM_OK;
+    if (top < 1 || N < 1 || K < 8 || K % 8 || ((uintptr_t)A & 15) || ((uintptr_t)B0 & 15) || ((uintptr_t)B1 & 15) ||
+        (size_t)K * sizeof(float) > 48 * 1024)
+        return CPM_BAD_ARGUMENT;
+    const dim3 grid(n_pairs, (N + kGemvFeatures - 1) / kGemvFeatures);
+    if (grid.y > 65535) return CPM_BAD_ARGUMENT;
+    if (gated)
+        cpm_launch(kLaunchProduct, moe_pair_gemv_kernel<true>, grid, dim3(256), (size_t)K * sizeof(float), stream, (const bf16*)A,
+                   (const bf16*)B0, (const bf16*)B1, (bf16*)C, chosen, top, N, K);
+    else
+        cpm_launch(kLaunchProduct, moe_pair_gemv_kernel<false>, grid, dim3(256), (size_t)K * sizeof(float), stream, (const bf16*)A,
+                   (const bf16*)B0, (const bf16*)B1, (bf16*)C, chosen, top, N, K);
+    return launch_status();
+}
+
 // out[t] = sum_k weights[t][k] * Y[t * top + k] + gate[t] * shared[t]
 template <typename T>
 __global__ void moe_combine_kernel(const T* __restrict__ Y, const float* __restrict__ weights, const T* __restrict__ shared,

@@ -84,6 +84,7 @@ _SIGNATURES = {
     "cpm_moe_route": [_P, c_int, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, _P],
     "cpm_moe_group": [_P, c_int, c_int, _P, _P, _P],
     "cpm_moe_expert_product": [_P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P],
+    "cpm_moe_pair_product": [_P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, _P],
     "cpm_moe_combine": [_P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, _P],
     "cpm_latent_attention_mma": [_P, _P, _P, c_int, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_float, c_int, _P],
 }

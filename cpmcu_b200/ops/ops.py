@@ -959,6 +959,8 @@ class Ops:
               f"moe_route ({n_experts} experts, top {top})")
         return chosen, weights, gate
 
+    MOE_PAIRWISE_MAX_PAIRS = int(os.environ.get("CPMCU_MOE_PAIRWISE_MAX", "96"))     # up to here a pair streams its expert alone
+
     def moe_experts(self, x: torch.Tensor, chosen: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor,
                     w_down: torch.Tensor) -> torch.Tensor:
         """x [tokens, hidden]; chosen int32 [tokens, top]; stacks w_gate, w_up [experts, ff, hidden], w_down [experts,
@@ -970,13 +972,21 @@ class Ops:
         top = chosen.shape[1]
         E, ff, _ = w_gate.shape
         pairs = n * top
+        h = self.empty(pairs, ff)
+        y = self.empty(pairs, hidden)
+        if (self.code == BF16 and pairs <= self.MOE_PAIRWISE_MAX_PAIRS and hidden % 8 == 0 and ff % 8 == 0
+                and hidden <= 12288 and ff <= 12288):
+            # few pairs (a decode step): every pair streams its expert's weights, no grouping
+            check(self.lib.cpm_moe_pair_product(_ptr(x), _ptr(w_gate), _ptr(w_up), _ptr(h), _ptr(chosen), pairs, top, ff, hidden, 1,
+                                                self._stream()), "moe gate/up product by pair")
+            check(self.lib.cpm_moe_pair_product(_ptr(h), _ptr(w_down), None, _ptr(y), _ptr(chosen), pairs, top, hidden, ff, 0,
+                                                self._stream()), "moe down product by pair")
+            return y
         offsets = self.empty(E + 1, dtype=torch.int32)
         order = self.empty(pairs, dtype=torch.int32)
         check(self.lib.cpm_moe_group(_ptr(chosen), pairs, E, _ptr(offsets), _ptr(order), self._stream()), "moe_group")
-        h = self.empty(pairs, ff)
         check(self.lib.cpm_moe_expert_product(_ptr(x), _ptr(w_gate), _ptr(w_up), _ptr(h), _ptr(offsets), _ptr(order), pairs, E, top,
                                               ff, hidden, 1, self.code, self._stream()), "moe gate/up product")
-        y = self.empty(pairs, hidden)
         check(self.lib.cpm_moe_expert_product(_ptr(h), _ptr(w_down), None, _ptr(y), _ptr(offsets), _ptr(order), pairs, E, top,
                                               hidden, ff, 0, self.code, self._stream()), "moe down product")
         return y
