@@ -757,7 +757,7 @@ def mufevik_config(z: dict) -> dict:
     par = {"type": "parallel", "mlp": mlp,
            "mixer": {"left": {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["vdim"],
                               "scale": z["dim"] ** -0.5, "rot": {"dims": z["dim"], "base": 10000.0}},
-                     "right": {"heads": z["lin_heads"], "dim": z["lin_dim"], "vdim": z["lin_vdim"], "tau": 16.0, "rank": 16}}}
+                     "right": {"heads": z["lin_heads"], "dim": z["lin_dim"], "vdim": z["lin_vdim"], "tau": 8.0, "rank": 32}}}
     delta = {"type": "delta", "mlp": mlp, "mixer": {"heads": z["delta_heads"], "kv_heads": z["delta_qk_heads"], "dim": z["delta_dim"],
                                                      "vdim": z["delta_vdim"], "conv": z["conv"]}}
     return {"architecture": "Mufevik", "vocab": z["vocab"], "width": z["width"], "streams": z["streams"], "logit_scale": 1.0,

@@ -378,7 +378,7 @@ decode_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_c
                         const int* __restrict__ kv_len, const int* __restrict__ slots,
                         const int* __restrict__ page_table, int max_pages, float* __restrict__ part_o,
                         float* __restrict__ part_ml, bf16* __restrict__ out, int n_heads, int n_kv, int m_tiles,
-                        int n_splits, float scale_log2, DecodeRope rope, int v_shift) {
+                        int n_splits, float scale_log2, DecodeRope rope, int v_shift, int v_runs) {
     // A block takes one share of a sequence's pages; its warps take every third page of the
     // share and merge their results in shared memory before anything is written.  With one share
     // per sequence the block writes the final result to ``out`` itself and no combine kernel follows.
@@ -387,7 +387,12 @@ decode_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_c
     __shared__ float sm_m[DecodeSmem<D>::kWarps][16], sm_l[DecodeSmem<D>::kWarps][16];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int split = blockIdx.x;
-    const int kvh = blockIdx.y / m_tiles, mt = blockIdx.y % m_tiles, b = blockIdx.z;
+    // v_runs > 1: the grid's z axis holds v_runs runs over the same sequences, run r with the values shifted by r heads;
+    // bv is the row of the output (run-major), b the sequence
+    const int kvh = blockIdx.y / m_tiles, mt = blockIdx.y % m_tiles, bv = blockIdx.z;
+    const int n_real = v_runs > 1 ? (int)gridDim.z / v_runs : (int)gridDim.z;
+    const int b = bv % n_real;
+    if (v_runs > 1) v_shift = bv / n_real;
     const int group = n_heads / n_kv;
     const int j = lane & 3, g = lane >> 2;
     pdl_launch_dependents();
@@ -494,7 +499,7 @@ decode_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_c
         sm_l[warp][g + 8] = st.l[1];
     }
     __syncthreads();
-    const int64_t unit = (((int64_t)b * n_kv + kvh) * m_tiles + mt) * n_splits + split;
+    const int64_t unit = (((int64_t)bv * n_kv + kvh) * m_tiles + mt) * n_splits + split;
     float* po = part_o + unit * 16 * D;
     for (int i = threadIdx.x; i < 16 * D; i += DecodeSmem<D>::kWarps * 32) {
         const int row = i / D, c = i - row * D;
@@ -512,7 +517,7 @@ decode_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_c
         if (n_splits == 1) {
             const int local = mt * 16 + row;
             if (local < group)
-                out[((int64_t)b * n_heads + kvh * group + local) * D + c] = __float2bfloat16_rn(l > 0.f ? o / l : 0.f);
+                out[((int64_t)bv * n_heads + kvh * group + local) * D + c] = __float2bfloat16_rn(l > 0.f ? o / l : 0.f);
             continue;
         }
         po[i] = o;
@@ -562,11 +567,14 @@ template <int D>
 static int launch_decode(const void* q, const void* k_cache, const void* v_cache, void* out, const int* kv_len,
                          const int* slots, const int* page_table, int max_pages, float* scratch, int n_seqs,
                          int n_heads, int n_kv, int n_splits, float scale, cudaStream_t stream,
-                         DecodeRope rope = DecodeRope{nullptr, nullptr, 1.f, 0, nullptr, nullptr, 0}, int v_shift = 0) {
+                         DecodeRope rope = DecodeRope{nullptr, nullptr, 1.f, 0, nullptr, nullptr, 0}, int v_shift = 0,
+                         int v_runs = 1) {
     const int m_tiles = (n_heads / n_kv + 15) / 16;
+    const int n_rows = n_seqs * (v_runs > 1 ? v_runs : 1);       // rows of the output: sequences, or runs x sequences
+    if (n_rows > 65535) return CPM_BAD_ARGUMENT;
     float* part_o = scratch;
-    float* part_ml = scratch + (int64_t)n_seqs * n_kv * m_tiles * n_splits * 16 * D;
-    dim3 grid(n_splits, n_kv * m_tiles, n_seqs);
+    float* part_ml = scratch + (int64_t)n_rows * n_kv * m_tiles * n_splits * 16 * D;
+    dim3 grid(n_splits, n_kv * m_tiles, n_rows);
     auto kern = decode_attention_kernel<D>;
     rope.early = g_decode_early;
     constexpr int smem = DecodeSmem<D>::kTotal;
@@ -574,9 +582,9 @@ static int launch_decode(const void* q, const void* k_cache, const void* v_cache
     if (int st = ensure_dynamic_smem(kern, smem, configured)) return st;
     cpm_launch(kLaunchAttention, kern, grid, DecodeSmem<D>::kWarps * 32, smem, stream, (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache,
                kv_len, slots, page_table, max_pages, part_o, part_ml, (bf16*)out, n_heads, n_kv, m_tiles, n_splits,
-               scale * 1.4426950408889634f, rope, v_shift);
+               scale * 1.4426950408889634f, rope, v_shift, v_runs);
     if (n_splits > 1)
-        cpm_launch(kLaunchCombine, combine_splits_kernel, dim3(n_heads, n_seqs), D >= 128 ? 128 : 64, 0, stream, (const float*)part_o,
+        cpm_launch(kLaunchCombine, combine_splits_kernel, dim3(n_heads, n_rows), D >= 128 ? 128 : 64, 0, stream, (const float*)part_o,
                    (const float*)part_ml, (bf16*)out, n_heads, n_kv, m_tiles, n_splits, (int)D);
     return launch_status();
 }
@@ -602,15 +610,19 @@ CPM_API int cpm_decode_attention_bf16(const void* q, const void* k_cache, const 
 CPM_API int cpm_decode_attention_bf16_vshift(const void* q, const void* k_cache, const void* v_cache, void* out,
                                              const int* kv_len, const int* slots, const int* page_table, int max_pages,
                                              float* scratch, int n_seqs, int n_heads, int n_kv, int d, int n_splits,
-                                             float scale, int v_shift, cudaStream_t stream) {
+                                             float scale, int v_shift, int v_runs, cudaStream_t stream) {
+    // v_runs > 1: one launch does runs 0 .. v_runs - 1 (v_shift is then not used); out is [v_runs, n_seqs, heads, d] and
+    // scratch holds cpm_decode_attention_scratch_floats(v_runs * n_seqs, ...) floats
     if (n_seqs <= 0) return CPM_OK;
-    if (n_kv <= 0 || n_heads % n_kv || n_splits < 1 || n_seqs > 65535 || !scratch || v_shift < 0 || v_shift >= n_kv) return CPM_BAD_ARGUMENT;
+    if (n_kv <= 0 || n_heads % n_kv || n_splits < 1 || n_seqs > 65535 || !scratch || v_shift < 0 || v_shift >= n_kv || v_runs < 1 ||
+        v_runs > n_kv)
+        return CPM_BAD_ARGUMENT;
     const DecodeRope none{nullptr, nullptr, 1.f, 0, nullptr, nullptr, 0};
     switch (d) {
-        case 32: return launch_decode<32>(q, k_cache, v_cache, out, kv_len, slots, page_table, max_pages, scratch, n_seqs, n_heads, n_kv, n_splits, scale, stream, none, v_shift);
-        case 64: return launch_decode<64>(q, k_cache, v_cache, out, kv_len, slots, page_table, max_pages, scratch, n_seqs, n_heads, n_kv, n_splits, scale, stream, none, v_shift);
-        case 96: return launch_decode<96>(q, k_cache, v_cache, out, kv_len, slots, page_table, max_pages, scratch, n_seqs, n_heads, n_kv, n_splits, scale, stream, none, v_shift);
-        case 128: return launch_decode<128>(q, k_cache, v_cache, out, kv_len, slots, page_table, max_pages, scratch, n_seqs, n_heads, n_kv, n_splits, scale, stream, none, v_shift);
+        case 32: return launch_decode<32>(q, k_cache, v_cache, out, kv_len, slots, page_table, max_pages, scratch, n_seqs, n_heads, n_kv, n_splits, scale, stream, none, v_shift, v_runs);
+        case 64: return launch_decode<64>(q, k_cache, v_cache, out, kv_len, slots, page_table, max_pages, scratch, n_seqs, n_heads, n_kv, n_splits, scale, stream, none, v_shift, v_runs);
+        case 96: return launch_decode<96>(q, k_cache, v_cache, out, kv_len, slots, page_table, max_pages, scratch, n_seqs, n_heads, n_kv, n_splits, scale, stream, none, v_shift, v_runs);
+        case 128: return launch_decode<128>(q, k_cache, v_cache, out, kv_len, slots, page_table, max_pages, scratch, n_seqs, n_heads, n_kv, n_splits, scale, stream, none, v_shift, v_runs);
         default: return CPM_BAD_ARGUMENT;
     }
 }

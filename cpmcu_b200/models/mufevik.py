@@ -13,7 +13,7 @@ from ..parts.base import LayerSpec, ModelSpec, PartSpec, default_schedule
 
 LAYER_NAMES = {"mixer_norm": "norm1", "feed_forward_norm": "norm2", "mixer": "mix.", "feed_forward": "mlp.",
                "hyper1": "hc1.", "hyper2": "hc2."}
-DEFAULT_DECAY_RANK = 16
+DEFAULT_DECAY_RANK = 32          # when neither the configuration nor a checkpoint gives it (random weights)
 
 
 def decay_rank(side) -> int:

@@ -74,7 +74,8 @@ _SIGNATURES = {
     "cpm_talking_attention": [_P, _P, _P, _P, _P, _P, _P, _P, c_int, _P, _P, c_int, c_int, c_int, c_int, c_int, c_float, c_int, _P],
     "cpm_scale_heads_bf16": [_P, _P, _P, c_int, c_int, c_int, _P],
     "cpm_talk_mix_bf16": [_P, _P, _P, c_int, c_int, c_int, c_int, _P],
-    "cpm_decode_attention_bf16_vshift": [_P, _P, _P, _P, _P, _P, _P, c_int, _P, c_int, c_int, c_int, c_int, c_int, c_float, c_int, _P],
+    "cpm_decode_attention_bf16_vshift": [_P, _P, _P, _P, _P, _P, _P, c_int, _P, c_int, c_int, c_int, c_int, c_int, c_float, c_int,
+                                         c_int, _P],
     "cpm_prefill_attention_bf16_vshift": [_P, _P, _P, _P, _P, _P, c_int, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_float,
                                           c_int, _P],
     "cpm_prefill_attention_tcgen05_vshift": [_P, _P, _P, _P, _P, _P, c_int, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int,

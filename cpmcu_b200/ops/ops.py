@@ -607,21 +607,25 @@ class Ops:
 
     def decode_attention(self, q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, kv_len: torch.Tensor,
                          slots: torch.Tensor, page_table: torch.Tensor, n_kv: int, scale: float,
-                         n_splits: Optional[int] = None, out: Optional[torch.Tensor] = None, v_shift: int = 0) -> torch.Tensor:
+                         n_splits: Optional[int] = None, out: Optional[torch.Tensor] = None, v_shift: int = 0,
+                         v_runs: int = 1) -> torch.Tensor:
         """One query token per sequence: q [seqs, heads, d] -> [seqs, heads*d].  ``v_shift``: the values come from
-        key-value head (kv head + v_shift) mod n_kv instead of the keys' own."""
+        key-value head (kv head + v_shift) mod n_kv instead of the keys' own.  ``v_runs`` > 1: one launch does the runs
+        with shifts 0 .. v_runs - 1; the result is [v_runs, seqs, heads*d]."""
         self._act(q, "q")
         n, n_heads, d = q.shape
+        rows = n * max(1, int(v_runs))
         if n_splits is None:
-            n_splits = self.decode_splits(n, n_heads, n_kv)
-        floats = self.lib.cpm_decode_attention_scratch_floats(n, n_heads, n_kv, d, n_splits)
+            n_splits = self.decode_splits(rows, n_heads, n_kv)
+        floats = self.lib.cpm_decode_attention_scratch_floats(rows, n_heads, n_kv, d, n_splits)
         scratch = self.empty(floats, dtype=torch.float32)
         if out is None:
-            out = self.empty(n, n_heads * d)
-        if v_shift:
+            out = self.empty(rows, n_heads * d) if v_runs <= 1 else self.empty(v_runs, n, n_heads * d)
+        if v_shift or v_runs > 1:
             check(self.lib.cpm_decode_attention_bf16_vshift(_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(kv_len),
                                                             _ptr(slots), _ptr(page_table), page_table.shape[1], _ptr(scratch),
-                                                            n, n_heads, n_kv, d, n_splits, float(scale), int(v_shift), self._stream()),
+                                                            n, n_heads, n_kv, d, n_splits, float(scale), int(v_shift),
+                                                            max(1, int(v_runs)), self._stream()),
                   f"decode attention (head_dim {d}, values shifted)")
         else:
             check(self.lib.cpm_decode_attention_bf16(_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(kv_len),
@@ -914,11 +918,11 @@ class Ops:
         on_tcgen05 = (not ctx.is_decode and self.use_tcgen05_attention and (n_heads // n_kv) % 2 == 0
                       and (d == 128 or (d == 64 and ctx.max_kv_len >= 1024)))
         shares = self.prefill_key_shares(ctx.q_lens, ctx.max_kv_len, n_heads) if on_tcgen05 else 1
-        for s in range(n_kv):
-            if ctx.is_decode:
-                self.decode_attention(qs, lane.k, lane.v, ctx.kv_len_dev, ctx.slot_dev, lane.page_table, n_kv, scale,
-                                      out=parts[s], v_shift=s)
-            elif on_tcgen05:
+        if ctx.is_decode:          # all runs in one launch (and one combination of the keys' shares)
+            self.decode_attention(qs, lane.k, lane.v, ctx.kv_len_dev, ctx.slot_dev, lane.page_table, n_kv, scale, out=parts,
+                                  v_runs=n_kv)
+        for s in range(n_kv if not ctx.is_decode else 0):
+            if on_tcgen05:
                 self.prefill_attention_tcgen05(qs, lane.k, lane.v, tiles, ctx.cu_q, ctx.kv_len_dev, ctx.slot_dev, lane.page_table,
                                                n_kv, scale, shares, out=parts[s], v_shift=s)
             else:

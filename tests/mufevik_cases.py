@@ -64,7 +64,7 @@ def config_c() -> dict:
     """A single stream that still goes through hyper-connections (``streams``: 1); a convolution of one tap."""
     return {"architecture": NAME, "vocab": 97, "width": 32, "streams": 1, "logit_scale": 2.0, "norm": {"eps": 1e-6},
             "layers": [
-                {"type": "parallel", "mixer": {"left": _left(6, 3, 8, 12, 0.35, (4, 20000.0)),
+                {"type": "parallel", "mixer": {"left": _left(6, 3, 8, 12, 0.35, (4, 30000.0)),
                                                 "right": {"heads": 2, "dim": 12, "vdim": 8, "tau": 30.0}},
                  "mlp": _moe(6, 2, 24, groups=(3, 1))},
                 {"type": "delta", "mixer": {"heads": 2, "kv_heads": 2, "dim": 16, "vdim": 24, "conv": 1}, "mlp": _moe(3, 2, 8, shared=8)},

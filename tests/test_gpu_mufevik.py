@@ -490,7 +490,7 @@ def test_convolution_reads_the_state_and_leaves_the_last_inputs(K):
                 _close(torch.cat([piece[j] for piece in got[i]]), want[i][j], "float32", tol32=2e-5)
 
 
-@pytest.mark.parametrize("E,top,groups,keep", [(12, 3, 2, 1), (8, 2, 4, 2), (9, 4, 3, 2), (6, 6, 1, 1), (64, 6, 8, 3), (300, 8, 1, 1)])
+@pytest.mark.parametrize("E,top,groups,keep", [(10, 3, 2, 1), (8, 2, 4, 2), (9, 4, 3, 2), (6, 6, 1, 1), (64, 6, 8, 3), (300, 8, 1, 1)])
 def test_routing_follows_the_rule(E, top, groups, keep):
     from cpmcu_b200.ops.ops import Ops
 
