@@ -32,11 +32,6 @@ __device__ __forceinline__ void cp_async_f32(float* smem_dst, const float* gmem_
     asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" :: "r"(dst), "l"(gmem_src) : "memory");
 }
 
-// Floats of one staging buffer: q and k [tile][d], the decay [tile][d] or [tile], v [tile][columns], beta [tile].
-static inline int recurrence_stage_floats(int d, bool vector_decay, int cols) {
-    return kRecTile * (2 * d + (vector_decay ? d : 1) + cols + 1);
-}
-
 template <int W>
 __device__ __forceinline__ float lanes_sum(float v) {      // over the W consecutive threads of a column
 #pragma unroll
@@ -44,9 +39,12 @@ __device__ __forceinline__ float lanes_sum(float v) {      // over the W consecu
     return v;
 }
 
-// kLanes threads share a column (8 for key sizes up to 64, 16 above: shorter chains of dependent products per token);
-// a block of 256 threads holds 256 / kLanes columns; PER key channels a thread.
-template <int kLanes, int PER, bool DELTA, bool VECTOR_DECAY>
+// kLanes threads share a column (8 for key sizes up to 64, 16 above: shorter chains of dependent products per token)
+// and hold PER key channels each; a thread works kCpt adjacent columns at once (the key, query and decay operands are
+// loaded once for all of them, and their chains of dependent instructions interleave); a block of 256 threads holds
+// 256 / kLanes * kCpt columns.  Staged rows are kLanes * PER floats wide and zero (decay: one) beyond d, so the walk
+// needs no bounds.
+template <int kLanes, int PER, int kCpt, bool DELTA, bool VECTOR_DECAY>
 __global__ void __launch_bounds__(kRecThreads)
 linear_recurrence_kernel(const float* __restrict__ q, const float* __restrict__ k, int64_t qk_stride,      // [tokens, qk_heads, d]
                          const float* __restrict__ v, int64_t v_stride,                                    // [tokens, heads, dv]
@@ -56,42 +54,49 @@ linear_recurrence_kernel(const float* __restrict__ q, const float* __restrict__ 
                          const int* __restrict__ slots, float* __restrict__ out,                           // [tokens, heads, dv]
                          int heads, int qk_heads, int d, int dv, float q_scale) {
     extern __shared__ float rec_smem[];
-    constexpr int kCols = kRecThreads / kLanes;
-    constexpr int kAcc = PER >= 8 ? 8 : 4;
+    constexpr int kCols = kRecThreads / kLanes * kCpt;           // columns of the block
+    constexpr int kWide = kLanes * PER;                          // floats of a staged row of key channels
+    constexpr int kAcc = PER >= 8 ? 4 : 2;
+    constexpr int kAWidth = VECTOR_DECAY ? kWide : 1;
+    constexpr int kStage = kRecTile * (2 * kWide + kAWidth + kCols + 1);
     pdl_launch_dependents();
+    // the staged rows' tails beyond d are never copied to: zero (decay: one) for good
+    for (int i = threadIdx.x; i < 2 * kStage; i += blockDim.x) {
+        const int at = i % kStage;
+        rec_smem[i] = (VECTOR_DECAY && at >= 2 * kRecTile * kWide && at < 3 * kRecTile * kWide) ? 1.f : 0.f;
+    }
     pdl_wait();
     const int lane = threadIdx.x % kLanes;
-    const int lcol = threadIdx.x / kLanes;
-    const int col0 = blockIdx.x * kCols, col = col0 + lcol;
+    const int lcol = (threadIdx.x / kLanes) * kCpt;              // first of the thread's columns inside the block
+    const int col0 = blockIdx.x * kCols;
     const int h = blockIdx.y, seq = blockIdx.z;
     const int t0 = cu_q[seq], t1 = cu_q[seq + 1];
     if (t1 <= t0) return;
-    const bool live = col < dv;
-    const int colc = live ? col : dv - 1;
     const int g = h / (heads / qk_heads);
-    float* st = state + (((int64_t)slots[seq] * heads + h) * d) * dv + colc;
+    float* st = state + (((int64_t)slots[seq] * heads + h) * d) * dv;
     const bool fresh = positions[t0] == 0;
-    float S[PER];
+    float S[kCpt][PER];
 #pragma unroll
-    for (int i = 0; i < PER; ++i) {
-        const int c = lane + kLanes * i;
-        S[i] = (c < d && !fresh) ? st[(int64_t)c * dv] : 0.f;
-    }
-    const int a_width = VECTOR_DECAY ? d : 1;
-    const int stage = kRecTile * (2 * d + a_width + kCols + 1);
+    for (int j = 0; j < kCpt; ++j)
+#pragma unroll
+        for (int i = 0; i < PER; ++i) {
+            const int c = lane + kLanes * i, col = col0 + lcol + j;
+            S[j][i] = (c < d && col < dv && !fresh) ? st[(int64_t)c * dv + col] : 0.f;
+        }
+    __syncthreads();
     // the operands of up to kRecTile tokens from ``tb`` on are asked for (asynchronous copies into buffer ``buf``)
     auto stage_in = [&](int tb, int buf) {
-        float* qs = rec_smem + buf * stage;
-        float* ks = qs + kRecTile * d;
-        float* as = ks + kRecTile * d;
-        float* vs = as + kRecTile * a_width;
+        float* qs = rec_smem + buf * kStage;
+        float* ks = qs + kRecTile * kWide;
+        float* as = ks + kRecTile * kWide;
+        float* vs = as + kRecTile * kAWidth;
         float* bs = vs + kRecTile * kCols;
         const int nt = min(kRecTile, t1 - tb);
         for (int i = threadIdx.x; i < nt * d; i += blockDim.x) {
             const int tok = i / d, c = i % d;
-            cp_async_f32(qs + i, q + (int64_t)(tb + tok) * qk_stride + (int64_t)g * d + c);
-            cp_async_f32(ks + i, k + (int64_t)(tb + tok) * qk_stride + (int64_t)g * d + c);
-            if (VECTOR_DECAY) cp_async_f32(as + i, decay + (int64_t)(tb + tok) * decay_stride + (int64_t)h * d + c);
+            cp_async_f32(qs + tok * kWide + c, q + (int64_t)(tb + tok) * qk_stride + (int64_t)g * d + c);
+            cp_async_f32(ks + tok * kWide + c, k + (int64_t)(tb + tok) * qk_stride + (int64_t)g * d + c);
+            if (VECTOR_DECAY) cp_async_f32(as + tok * kWide + c, decay + (int64_t)(tb + tok) * decay_stride + (int64_t)h * d + c);
         }
         for (int i = threadIdx.x; i < nt * kCols; i += blockDim.x) {
             const int tok = i / kCols, c = min(col0 + i % kCols, dv - 1);
@@ -105,75 +110,119 @@ linear_recurrence_kernel(const float* __restrict__ q, const float* __restrict__ 
     };
     stage_in(t0, 0);
     int buf = 0;
+    // The read-out of a token is summed over the column's threads one token late, in the same shuffle rounds as the
+    // next token's S^T k: only that sum lies on the chain from one token's state to the next, and a warp that waits for
+    // one round of shuffles waits for both.
+    float pend[kCpt];
+#pragma unroll
+    for (int j = 0; j < kCpt; ++j) pend[j] = 0.f;
+    int64_t pend_row = -1;
     for (int tb = t0; tb < t1; tb += kRecTile, buf ^= 1) {
         asm volatile("cp.async.wait_group 0;" ::: "memory");
         __syncthreads();                                         // this tile has arrived; the other buffer is free again
         if (tb + kRecTile < t1) stage_in(tb + kRecTile, buf ^ 1);
-        const float* qs = rec_smem + buf * stage;
-        const float* ks = qs + kRecTile * d;
-        const float* as = ks + kRecTile * d;
-        const float* vs = as + kRecTile * a_width;
-        const float* bs = vs + kRecTile * kCols;
+        const float* qs = rec_smem + buf * kStage + lane;
+        const float* ks = qs + kRecTile * kWide;
+        const float* as = ks + kRecTile * kWide;
+        const float* vs = rec_smem + buf * kStage + kRecTile * (2 * kWide + kAWidth) + lcol;
+        const float* bs = rec_smem + buf * kStage + kRecTile * (2 * kWide + kAWidth + kCols);
         const int nt = min(kRecTile, t1 - tb);
-        for (int tok = 0; tok < nt; ++tok) {
-            float ck[PER], cq[PER];
-            const float cv = vs[tok * kCols + lcol];
-            const float a1 = VECTOR_DECAY ? 1.f : as[tok];
+        auto step = [&](int tok) {
+            float ck[PER], cq[PER], u[kCpt];
+            const float a1 = VECTOR_DECAY ? 1.f : as[tok - lane];
 #pragma unroll
             for (int i = 0; i < PER; ++i) {
-                const int c = lane + kLanes * i;
-                ck[i] = c < d ? ks[tok * d + c] : 0.f;
-                cq[i] = c < d ? qs[tok * d + c] : 0.f;
-                S[i] *= VECTOR_DECAY ? (c < d ? as[tok * d + c] : 1.f) : a1;
-            }
-            float u = cv;
-            if (DELTA) {
-                float dot[kAcc] = {};                          // partial sums: short chains of dependent products
+                ck[i] = ks[tok * kWide + kLanes * i];
+                cq[i] = qs[tok * kWide + kLanes * i];
+                const float a = VECTOR_DECAY ? as[tok * kWide + kLanes * i] : a1;
 #pragma unroll
-                for (int i = 0; i < PER; ++i) dot[i % kAcc] = fmaf(S[i], ck[i], dot[i % kAcc]);
+                for (int j = 0; j < kCpt; ++j) S[j][i] *= a;
+            }
+#pragma unroll
+            for (int j = 0; j < kCpt; ++j) u[j] = vs[tok * kCols + j];
+            float dot[kCpt][kAcc] = {};                         // partial sums: short chains of dependent products
+            if (DELTA) {
+#pragma unroll
+                for (int i = 0; i < PER; ++i)
+#pragma unroll
+                    for (int j = 0; j < kCpt; ++j) dot[j][i % kAcc] = fmaf(S[j][i], ck[i], dot[j][i % kAcc]);
+#pragma unroll
+                for (int j = 0; j < kCpt; ++j)
+#pragma unroll
+                    for (int w = kAcc / 2; w > 0; w >>= 1)
+#pragma unroll
+                        for (int i = 0; i < w; ++i) dot[j][i] += dot[j][i + w];
+            }
+#pragma unroll
+            for (int o = 1; o < kLanes; o <<= 1)
+#pragma unroll
+                for (int j = 0; j < kCpt; ++j) {
+                    if (DELTA) dot[j][0] += __shfl_xor_sync(0xffffffffu, dot[j][0], o);
+                    pend[j] += __shfl_xor_sync(0xffffffffu, pend[j], o);
+                }
+            if (pend_row >= 0 && lane == 0) {
+#pragma unroll
+                for (int j = 0; j < kCpt; ++j)
+                    if (col0 + lcol + j < dv) out[(pend_row * heads + h) * dv + col0 + lcol + j] = pend[j] * q_scale;
+            }
+            if (DELTA) {
+                const float b = bs[tok];
+#pragma unroll
+                for (int j = 0; j < kCpt; ++j) u[j] = b * (u[j] - dot[j][0]);
+            }
+            float op[kCpt][kAcc] = {};
+#pragma unroll
+            for (int i = 0; i < PER; ++i)
+#pragma unroll
+                for (int j = 0; j < kCpt; ++j) {
+                    S[j][i] = fmaf(ck[i], u[j], S[j][i]);
+                    op[j][i % kAcc] = fmaf(S[j][i], cq[i], op[j][i % kAcc]);
+                }
+#pragma unroll
+            for (int j = 0; j < kCpt; ++j) {
 #pragma unroll
                 for (int w = kAcc / 2; w > 0; w >>= 1)
 #pragma unroll
-                    for (int i = 0; i < w; ++i) dot[i] += dot[i + w];
-                u = bs[tok] * (cv - lanes_sum<kLanes>(dot[0]));
+                    for (int i = 0; i < w; ++i) op[j][i] += op[j][i + w];
+                pend[j] = op[j][0];
             }
-            float op[kAcc] = {};
+            pend_row = tb + tok;
+        };
+        if (nt == kRecTile) {                                    // a full tile: unrolled, so that later tokens' operands are loaded early
 #pragma unroll
-            for (int i = 0; i < PER; ++i) {
-                S[i] = fmaf(ck[i], u, S[i]);
-                op[i % kAcc] = fmaf(S[i], cq[i], op[i % kAcc]);
-            }
-#pragma unroll
-            for (int w = kAcc / 2; w > 0; w >>= 1)
-#pragma unroll
-                for (int i = 0; i < w; ++i) op[i] += op[i + w];
-            const float o = lanes_sum<kLanes>(op[0]);
-            if (lane == 0 && live) out[((int64_t)(tb + tok) * heads + h) * dv + col] = o * q_scale;
+            for (int tok = 0; tok < kRecTile; ++tok) step(tok);
+        } else {
+            for (int tok = 0; tok < nt; ++tok) step(tok);
         }
     }
-    if (live) {
+#pragma unroll
+    for (int j = 0; j < kCpt; ++j) {                             // the last token's read-out
+        const float o = lanes_sum<kLanes>(pend[j]);
+        if (lane == 0 && col0 + lcol + j < dv) out[(pend_row * heads + h) * dv + col0 + lcol + j] = o * q_scale;
+    }
+#pragma unroll
+    for (int j = 0; j < kCpt; ++j)
 #pragma unroll
         for (int i = 0; i < PER; ++i) {
-            const int c = lane + kLanes * i;
-            if (c < d) st[(int64_t)c * dv] = S[i];
+            const int c = lane + kLanes * i, col = col0 + lcol + j;
+            if (c < d && col < dv) st[(int64_t)c * dv + col] = S[j][i];
         }
-    }
 }
 
-template <int LANES, int PER>
+template <int LANES, int PER, int CPT>
 static void launch_recurrence(bool delta, bool vector_decay, cudaStream_t stream, const float* q, const float* k,
                               int64_t qk_stride, const float* v, int64_t v_stride, const float* decay, int64_t decay_stride,
                               const float* beta, int64_t beta_stride, float* state, const int* positions, const int* cu_q,
                               const int* slots, float* out, int n_seqs, int heads, int qk_heads, int d, int dv, float q_scale) {
-    constexpr int cols = kRecThreads / LANES;
+    constexpr int cols = kRecThreads / LANES * CPT;
     const dim3 grid((dv + cols - 1) / cols, heads, n_seqs), block(kRecThreads);
-    const size_t smem = 2 * (size_t)recurrence_stage_floats(d, vector_decay, cols) * sizeof(float);      // two buffers
+    const size_t smem = 2 * (size_t)kRecTile * (2 * LANES * PER + (vector_decay ? LANES * PER : 1) + cols + 1) * sizeof(float);
 #define CPM_REC(D, V) do {                                                                                                          \
         static bool configured[kMaxDevices] = {};                                                                                   \
-        if (smem > 48 * 1024 && ensure_dynamic_smem(linear_recurrence_kernel<LANES, PER, D, V>, 100 * 1024, configured) != CPM_OK)  \
-            return;                                                                                                                 \
-        cpm_launch(kLaunchAttention, linear_recurrence_kernel<LANES, PER, D, V>, grid, block, smem, stream, q, k, qk_stride, v,     \
-                   v_stride, decay, decay_stride, beta, beta_stride, state, positions, cu_q, slots, out, heads, qk_heads, d, dv,    \
+        if (smem > 48 * 1024 &&                                                                                                     \
+            ensure_dynamic_smem(linear_recurrence_kernel<LANES, PER, CPT, D, V>, 100 * 1024, configured) != CPM_OK) return;         \
+        cpm_launch(kLaunchAttention, linear_recurrence_kernel<LANES, PER, CPT, D, V>, grid, block, smem, stream, q, k, qk_stride,   \
+                   v, v_stride, decay, decay_stride, beta, beta_stride, state, positions, cu_q, slots, out, heads, qk_heads, d, dv, \
                    q_scale);                                                                                                        \
     } while (0)
     if (delta && vector_decay) CPM_REC(true, true);
@@ -183,11 +232,10 @@ static void launch_recurrence(bool delta, bool vector_decay, cudaStream_t stream
 #undef CPM_REC
 }
 
-static int g_recurrence_lanes = 8;
-// How many threads share a value column: 8 up to a key size of 64 and 16 above (the default), or, when set to 4, four
-// (measured slower at 2,048 tokens: 1,285 against 783 us for 16 heads of 128 x 128).
-CPM_API int cpm_set_recurrence_lanes(int lanes) {
-    g_recurrence_lanes = lanes;
+static int g_recurrence_columns = 1;
+// Columns a thread works at once: 1 (default) or 2 (measured slower on a prompt: 857 against 749 us for 16 heads of 128 x 128).
+CPM_API int cpm_set_recurrence_columns(int n) {
+    g_recurrence_columns = n;
     return CPM_OK;
 }
 
@@ -202,21 +250,15 @@ CPM_API int cpm_linear_recurrence(const float* q, const float* k, int64_t qk_str
     if (n_seqs <= 0) return CPM_OK;
     if (heads < 1 || qk_heads < 1 || heads % qk_heads || d < 1 || dv < 1 || d > 256) return CPM_BAD_ARGUMENT;
     const bool delta = beta != nullptr;
-#define CPM_REC_PER(L, P) launch_recurrence<L, P>(delta, vector_decay != 0, stream, q, k, qk_stride, v, v_stride, decay, decay_stride, \
-                                                  beta, beta_stride, state, positions, cu_q, slots, out, n_seqs, heads, qk_heads, d,  \
-                                                  dv, q_scale)
-    const int lanes = g_recurrence_lanes;
-    if (lanes == 4) {
-        if (d <= 32) CPM_REC_PER(4, 8);
-        else if (d <= 64) CPM_REC_PER(4, 16);
-        else if (d <= 128) CPM_REC_PER(4, 32);
-        else CPM_REC_PER(8, 32);
-    } else {
-        if (d <= 32) CPM_REC_PER(8, 4);
-        else if (d <= 64) CPM_REC_PER(8, 8);
-        else if (d <= 128) CPM_REC_PER(16, 8);
-        else CPM_REC_PER(16, 16);
-    }
+#define CPM_REC_PER(L, P, C) launch_recurrence<L, P, C>(delta, vector_decay != 0, stream, q, k, qk_stride, v, v_stride, decay,        \
+                                                        decay_stride, beta, beta_stride, state, positions, cu_q, slots, out, n_seqs, \
+                                                        heads, qk_heads, d, dv, q_scale)
+    // two columns a thread where that still leaves blocks enough (a decode batch, or value heads of 64 and more)
+    const bool two = g_recurrence_columns == 2 && dv >= 32;
+    if (d <= 32) { if (two) CPM_REC_PER(8, 4, 2); else CPM_REC_PER(8, 4, 1); }
+    else if (d <= 64) { if (two) CPM_REC_PER(8, 8, 2); else CPM_REC_PER(8, 8, 1); }
+    else if (d <= 128) { if (two) CPM_REC_PER(16, 8, 2); else CPM_REC_PER(16, 8, 1); }
+    else { if (two) CPM_REC_PER(16, 16, 2); else CPM_REC_PER(16, 16, 1); }
 #undef CPM_REC_PER
     return launch_status();
 }

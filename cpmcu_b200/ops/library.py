@@ -81,7 +81,7 @@ _SIGNATURES = {
     "cpm_prefill_attention_tcgen05_vshift": [_P, _P, _P, _P, _P, _P, c_int, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int,
                                              c_float, _P, c_int, c_int, _P],
     "cpm_set_moe_tensor_cores": [c_int],
-    "cpm_set_recurrence_lanes": [c_int],
+    "cpm_set_recurrence_columns": [c_int],
     "cpm_moe_route": [_P, c_int, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, _P],
     "cpm_moe_group": [_P, c_int, c_int, _P, _P, _P],
     "cpm_moe_expert_product": [_P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P],
