@@ -39,7 +39,7 @@ __device__ __forceinline__ float lanes_sum(float v) {      // over the W consecu
     return v;
 }
 
-// kLanes threads share a column (8 for key sizes up to 64, 16 above: shorter chains of dependent products per token)
+// kLanes threads share a column (8 for key sizes up to 32, 16 above: shorter chains of dependent products per token)
 // and hold PER key channels each; a thread works kCpt adjacent columns at once (the key, query and decay operands are
 // loaded once for all of them, and their chains of dependent instructions interleave); a block of 256 threads holds
 // 256 / kLanes * kCpt columns.  Staged rows are kLanes * PER floats wide and zero (decay: one) beyond d, so the walk
@@ -256,7 +256,7 @@ CPM_API int cpm_linear_recurrence(const float* q, const float* k, int64_t qk_str
     // two columns a thread where that still leaves blocks enough (a decode batch, or value heads of 64 and more)
     const bool two = g_recurrence_columns == 2 && dv >= 32;
     if (d <= 32) { if (two) CPM_REC_PER(8, 4, 2); else CPM_REC_PER(8, 4, 1); }
-    else if (d <= 64) { if (two) CPM_REC_PER(8, 8, 2); else CPM_REC_PER(8, 8, 1); }
+    else if (d <= 64) { if (two) CPM_REC_PER(16, 4, 2); else CPM_REC_PER(16, 4, 1); }      // 451 us against 505 with 8 threads of 8 channels
     else if (d <= 128) { if (two) CPM_REC_PER(16, 8, 2); else CPM_REC_PER(16, 8, 1); }
     else { if (two) CPM_REC_PER(16, 16, 2); else CPM_REC_PER(16, 16, 1); }
 #undef CPM_REC_PER
