@@ -8,13 +8,13 @@
 //
 // The mix needs every head's *normalised* weight of a key, so a query is worked in two walks over its keys: the
 // first finds every head's maximum and sum, the second forms p_g for 32 keys at a time in shared memory, mixes
-// them and adds the values.  One block per query token, one warp per head; a lane owns a key in the scores and a
+// them and adds the values.  One block per query token, one warp per head (beyond 32 heads a warp works several); a lane owns a key in the scores and a
 // set of value channels in the weighted sum (value pages are [kv_head][dv][token], so 32 keys of a channel are
 // contiguous).  Scores, weights and sums are fp32; q, the cache and the output have the storage type.  Key size d
 // and value size dv are independent.
 #include "common.cuh"
 
-constexpr int kTalkMaxHeads = 32;
+constexpr int kTalkMaxHeads = 128;
 constexpr int kTalkMaxVPerLane = 8;      // dv <= 256
 
 template <typename T>
@@ -44,8 +44,9 @@ __device__ __forceinline__ float key_dot<bf16>(const bf16* __restrict__ krow, co
     return dot;
 }
 
-template <typename T>
-__global__ void talking_attention_kernel(const T* __restrict__ q,            // [tokens, heads, d]
+// HPW: heads a warp works: 1 up to 32 heads (a warp each); more heads go round 16 warps.
+template <typename T, int HPW>
+__global__ void __launch_bounds__(HPW == 1 ? 1024 : 512) talking_attention_kernel(const T* __restrict__ q,            // [tokens, heads, d]
                                          const T* __restrict__ k_cache, const T* __restrict__ v_cache,
                                          T* __restrict__ out,                // [tokens, heads, dv]
                                          const int* __restrict__ positions, const int* __restrict__ token_seq,
@@ -59,72 +60,110 @@ __global__ void talking_attention_kernel(const T* __restrict__ q,            // 
     pdl_launch_dependents();
     for (int i = threadIdx.x; i < n_heads * n_heads; i += blockDim.x) tk[i] = talk[i];
     pdl_wait();
-    const int g = threadIdx.x >> 5, lane = threadIdx.x & 31;       // this warp's head
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n_warps = blockDim.x >> 5;
     const int t = blockIdx.x;
     const int p = positions[t];
     const int* pages = page_table + (int64_t)slots[token_seq[t]] * max_pages;
-    const int kvh = g / (n_heads / n_kv);
-    const float s_scale = scale * temp[g];
-    {
-        const T* qrow = q + ((int64_t)t * n_heads + g) * d;
-        for (int c = lane; c < d; c += 32) qs[g * d + c] = to_f32(qrow[c]);
-    }
+    const int rep = n_heads / n_kv;
+    for (int i = threadIdx.x; i < n_heads * d; i += blockDim.x) qs[i] = to_f32(q[(int64_t)t * n_heads * d + i]);
     __syncthreads();
-    const float* qg = qs + g * d;
 
-    // first walk: this head's maximum and sum
-    float m = -INFINITY, l = 0.f;
-    for (int j0 = 0; j0 <= p; j0 += 32) {
-        const int j = j0 + lane;
-        if (j <= p) {
-            const int page = CPM_PAGE(pages, j / kPageTokens, max_pages);
-            const float s = key_dot(k_cache + page_row_offset(page, kvh, j % kPageTokens, n_kv, d), qg, d) * s_scale;
-            const float m_new = fmaxf(m, s);
-            l = l * expf(m - m_new) + expf(s - m_new);       // expf(-inf) = 0 at the first key
-            m = m_new;
+    // first walk: every head's maximum and sum
+    float M[HPW], inv_L[HPW], s_scale[HPW];
+#pragma unroll
+    for (int hi = 0; hi < HPW; ++hi) {
+        const int g = warp + hi * n_warps;
+        M[hi] = 0.f;
+        inv_L[hi] = 0.f;
+        s_scale[hi] = 0.f;
+        if (g >= n_heads) continue;
+        const int kvh = g / rep;
+        const float* qg = qs + g * d;
+        s_scale[hi] = scale * temp[g];
+        float m = -INFINITY, l = 0.f;
+        for (int j0 = 0; j0 <= p; j0 += 32) {
+            const int j = j0 + lane;
+            if (j <= p) {
+                const int page = CPM_PAGE(pages, j / kPageTokens, max_pages);
+                const float s = key_dot(k_cache + page_row_offset(page, kvh, j % kPageTokens, n_kv, d), qg, d) * s_scale[hi];
+                const float m_new = fmaxf(m, s);
+                l = l * expf(m - m_new) + expf(s - m_new);       // expf(-inf) = 0 at the first key
+                m = m_new;
+            }
         }
+        M[hi] = warp_max(m);
+        inv_L[hi] = 1.0f / warp_sum(m == -INFINITY ? 0.f : l * expf(m - M[hi]));
     }
-    const float M = warp_max(m);
-    const float L = warp_sum(m == -INFINITY ? 0.f : l * expf(m - M));
-    const float inv_L = 1.0f / L;
 
     // second walk: normalised weights of 32 keys, mixed across heads, times the values
-    float acc[kTalkMaxVPerLane];
+    float acc[HPW][kTalkMaxVPerLane];
 #pragma unroll
-    for (int i = 0; i < kTalkMaxVPerLane; ++i) acc[i] = 0.f;
+    for (int hi = 0; hi < HPW; ++hi)
+#pragma unroll
+        for (int i = 0; i < kTalkMaxVPerLane; ++i) acc[hi][i] = 0.f;
     for (int j0 = 0; j0 <= p; j0 += 32) {
         const int j = j0 + lane;
-        float pr = 0.f;
         const int page0 = CPM_PAGE(pages, j0 / kPageTokens, max_pages);      // 32 keys from a multiple of 32 lie in one page
-        if (j <= p) {
-            const float s = key_dot(k_cache + page_row_offset(page0, kvh, j % kPageTokens, n_kv, d), qg, d) * s_scale;
-            pr = expf(s - M) * inv_L;
-        }
-        P[g * 32 + lane] = pr;
-        __syncthreads();
-        float w = 0.f;
-        for (int gg = 0; gg < n_heads; ++gg) w = fmaf(tk[g * n_heads + gg], P[gg * 32 + lane], w);
-        const int n_here = min(32, p + 1 - j0);
-        const T* vbase = v_cache + value_offset(page0, kvh, 0, j0 % kPageTokens, n_kv, dv);
-        for (int jj = 0; jj < n_here; ++jj) {
-            const float wj = __shfl_sync(0xffffffffu, w, jj);
 #pragma unroll
-            for (int i = 0; i < kTalkMaxVPerLane; ++i) {
-                const int c = lane + 32 * i;
-                if (c < dv) acc[i] = fmaf(wj, to_f32(vbase[(int64_t)c * kPageTokens + jj]), acc[i]);
+        for (int hi = 0; hi < HPW; ++hi) {
+            const int g = warp + hi * n_warps;
+            if (g >= n_heads) continue;
+            float pr = 0.f;
+            if (j <= p) {
+                const float s = key_dot(k_cache + page_row_offset(page0, g / rep, j % kPageTokens, n_kv, d), qs + g * d, d) * s_scale[hi];
+                pr = expf(s - M[hi]) * inv_L[hi];
+            }
+            P[g * 32 + lane] = pr;
+        }
+        __syncthreads();
+        const int n_here = min(32, p + 1 - j0);
+#pragma unroll
+        for (int hi = 0; hi < HPW; ++hi) {
+            const int h = warp + hi * n_warps;
+            if (h >= n_heads) continue;
+            float w = 0.f;
+            for (int gg = 0; gg < n_heads; ++gg) w = fmaf(tk[h * n_heads + gg], P[gg * 32 + lane], w);
+            const T* vbase = v_cache + value_offset(page0, h / rep, 0, j0 % kPageTokens, n_kv, dv);
+            for (int jj = 0; jj < n_here; ++jj) {
+                const float wj = __shfl_sync(0xffffffffu, w, jj);
+#pragma unroll
+                for (int i = 0; i < kTalkMaxVPerLane; ++i) {
+                    const int c = lane + 32 * i;
+                    if (c < dv) acc[hi][i] = fmaf(wj, to_f32(vbase[(int64_t)c * kPageTokens + jj]), acc[hi][i]);
+                }
             }
         }
         __syncthreads();
     }
-    T* orow = out + ((int64_t)t * n_heads + g) * dv;
 #pragma unroll
-    for (int i = 0; i < kTalkMaxVPerLane; ++i) {
-        const int c = lane + 32 * i;
-        if (c < dv) orow[c] = from_f32<T>(acc[i]);
+    for (int hi = 0; hi < HPW; ++hi) {
+        const int h = warp + hi * n_warps;
+        if (h >= n_heads) continue;
+        T* orow = out + ((int64_t)t * n_heads + h) * dv;
+#pragma unroll
+        for (int i = 0; i < kTalkMaxVPerLane; ++i) {
+            const int c = lane + 32 * i;
+            if (c < dv) orow[c] = from_f32<T>(acc[hi][i]);
+        }
     }
 }
 
-static bool g_talk_smem_done_bf16[kMaxDevices], g_talk_smem_done_f32[kMaxDevices];
+template <typename T, int HPW>
+static int launch_talking(const void* q, const void* k_cache, const void* v_cache, void* out, const int* positions,
+                          const int* token_seq, const int* slots, const int* page_table, int max_pages, const float* temp,
+                          const float* talk, int n_tokens, int n_heads, int n_kv, int d, int dv, float scale, size_t smem,
+                          cudaStream_t stream) {
+    static bool configured[kMaxDevices] = {};            // per kernel and per device
+    if (smem > 48 * 1024) {
+        const int e = ensure_dynamic_smem(talking_attention_kernel<T, HPW>, 200 * 1024, configured);
+        if (e != CPM_OK) return e;
+    }
+    const int warps = HPW == 1 ? n_heads : 16;
+    cpm_launch(kLaunchAttention, talking_attention_kernel<T, HPW>, dim3(n_tokens), dim3(32 * warps), smem, stream, (const T*)q,
+               (const T*)k_cache, (const T*)v_cache, (T*)out, positions, token_seq, slots, page_table, max_pages, temp, talk, n_heads,
+               n_kv, d, dv, scale);
+    return launch_status();
+}
 
 CPM_API int cpm_talking_attention(const void* q, const void* k_cache, const void* v_cache, void* out, const int* positions,
                                   const int* token_seq, const int* slots, const int* page_table, int max_pages,
@@ -135,25 +174,11 @@ CPM_API int cpm_talking_attention(const void* q, const void* k_cache, const void
         return CPM_BAD_ARGUMENT;
     const size_t smem = (size_t)(n_heads * d + n_heads * 32 + n_heads * n_heads) * sizeof(float);
     if (smem > 200 * 1024) return CPM_BAD_ARGUMENT;
-    const dim3 grid(n_tokens), block(32 * n_heads);
-    if (dtype == CPM_BF16) {
-        if (smem > 48 * 1024) {
-            const int e = ensure_dynamic_smem(talking_attention_kernel<bf16>, 200 * 1024, g_talk_smem_done_bf16);
-            if (e != CPM_OK) return e;
-        }
-        cpm_launch(kLaunchAttention, talking_attention_kernel<bf16>, grid, block, smem, stream, (const bf16*)q, (const bf16*)k_cache,
-                   (const bf16*)v_cache, (bf16*)out, positions, token_seq, slots, page_table, max_pages, temp, talk, n_heads, n_kv,
-                   d, dv, scale);
-    } else {
-        if (smem > 48 * 1024) {
-            const int e = ensure_dynamic_smem(talking_attention_kernel<float>, 200 * 1024, g_talk_smem_done_f32);
-            if (e != CPM_OK) return e;
-        }
-        cpm_launch(kLaunchAttention, talking_attention_kernel<float>, grid, block, smem, stream, (const float*)q,
-                   (const float*)k_cache, (const float*)v_cache, (float*)out, positions, token_seq, slots, page_table, max_pages,
-                   temp, talk, n_heads, n_kv, d, dv, scale);
-    }
-    return launch_status();
+#define CPM_TALK(TT, HPW) launch_talking<TT, HPW>(q, k_cache, v_cache, out, positions, token_seq, slots, page_table, max_pages, temp, \
+                                                  talk, n_tokens, n_heads, n_kv, d, dv, scale, smem, stream)
+    if (dtype == CPM_BF16) return n_heads <= 32 ? CPM_TALK(bf16, 1) : n_heads <= 64 ? CPM_TALK(bf16, 4) : CPM_TALK(bf16, 8);
+    return n_heads <= 32 ? CPM_TALK(float, 1) : n_heads <= 64 ? CPM_TALK(float, 4) : CPM_TALK(float, 8);
+#undef CPM_TALK
 }
 
 // ---------------------------------------------------------------------------

@@ -31,8 +31,8 @@ class TalkingHeadsAttention(Mixer):
         super().__init__(ops)
         if n_heads % n_kv_heads:
             raise ValueError(f"{n_heads} heads cannot be grouped over {n_kv_heads} key-value heads")
-        if n_heads > 32 or value_dim > 256:
-            raise ValueError("talking_heads_attention: the kernel takes up to 32 heads and value heads of up to 256 channels")
+        if n_heads > 128 or value_dim > 256:
+            raise ValueError("talking_heads_attention: the kernel takes up to 128 heads and value heads of up to 256 channels")
         self.hidden_size, self.n_heads, self.n_kv = int(hidden_size), int(n_heads), int(n_kv_heads)
         self.d, self.dv, self.scale = int(head_dim), int(value_dim), float(softmax_scale)
         self.position = build_part(POSITIONS, position, ops)

@@ -346,7 +346,7 @@ def _attention_reference(q, k, v, temp, talk, scale, rot):
 @pytest.mark.parametrize("generic", [True, False])
 @pytest.mark.parametrize("H,G,d,dv,rot", [(4, 2, 24, 40, (16, 5000.0)), (5, 5, 12, 36, (6, 777.0)), (1, 1, 64, 64, (64, 10000.0)),
                                           (6, 3, 8, 12, None), (32, 8, 128, 128, (64, 1e6)), (8, 4, 64, 64, (32, 1e4)),
-                                          (6, 3, 96, 96, None), (3, 3, 32, 32, (32, 50.0))])
+                                          (6, 3, 96, 96, None), (3, 3, 32, 32, (32, 50.0)), (40, 10, 16, 24, (8, 300.0)), (66, 66, 8, 8, None)])
 def test_talking_attention_sees_every_key_up_to_the_query_and_mixes_heads(dtype, H, G, d, dv, rot, generic):
     """For chosen (query, key) pairs one score towers over the others: the first key, a key far back, the keys on both
     sides of a page border and the query itself; right after the query stands a still larger key that must stay
